@@ -68,3 +68,67 @@ def build_decode_batch(decode_seqs: Sequence[int], token_histories: Dict[int, Se
         bt[i, :len(s.block_table)] = s.block_table
     return DecodeBatch([s.seq_id for s in data], np.asarray([[s.last_token] for s in data], dtype=np.int64),
                        np.asarray([s.slot for s in data], dtype=np.int32), bt, max(s.seq_len for s in data))
+
+
+# ------------------------------------------------------------------------------------------------------------------------------
+# flat mixed steps: prompt portions beside single decoded tokens (the chunked-prefill batches of reference
+# src/engine/batch_engine.rs:172-272 and the decode batches above, as one token list)
+# ------------------------------------------------------------------------------------------------------------------------------
+@dataclass
+class StepEntry:
+    """the next tokens of one request"""
+    tokens: Sequence[int]
+    pos0: int                   # position of tokens[0] in its sequence
+    slot: int                   # recurrent-state slot of the request
+    block_table: Sequence[int]  # KV pages of the request (must cover pos0 + len(tokens) positions)
+    want: Sequence[int] = ()    # indices into `tokens` whose logits are wanted
+
+
+@dataclass
+class StepArrays:
+    """int32 arrays of one step (include/b200seq.h: b200seq_step), host side"""
+    tok_ids: np.ndarray
+    tok_ent: np.ndarray
+    tok_pos: np.ndarray
+    ent_start: np.ndarray
+    ent_slot: np.ndarray
+    ent_pos0: np.ndarray
+    block_table: np.ndarray    # [B, max_blocks]
+    want_rows: np.ndarray      # token rows whose logits are wanted, in entry order
+    T: int
+    B: int
+
+    @property
+    def decode_only(self) -> bool:
+        return self.T == self.B
+
+
+def build_step(entries: Sequence[StepEntry], block_size: int, max_blocks: Optional[int] = None) -> StepArrays:
+    B = len(entries)
+    lens = [len(e.tokens) for e in entries]
+    if any(n < 1 for n in lens):
+        raise ValueError("an entry without tokens")
+    T = int(sum(lens))
+    need = [-(-(e.pos0 + n) // block_size) for e, n in zip(entries, lens)]
+    for e, nb in zip(entries, need):
+        if len(e.block_table) < nb:
+            raise ValueError(f"block table of {len(e.block_table)} pages does not cover {nb} pages")
+    mb = max(need) if max_blocks is None else max_blocks
+    if mb < max(need):
+        raise ValueError("max_blocks too small for this step")
+    start = np.zeros(B + 1, dtype=np.int32)
+    start[1:] = np.cumsum(lens)
+    bt = np.zeros((B, mb), dtype=np.int32)
+    want: List[int] = []
+    for i, (e, nb) in enumerate(zip(entries, need)):
+        bt[i, :nb] = np.asarray(e.block_table[:nb], dtype=np.int32)
+        for w in e.want:
+            if not 0 <= w < lens[i]:
+                raise ValueError("a wanted place outside its entry")
+            want.append(int(start[i]) + int(w))
+    return StepArrays(
+        tok_ids=np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries]) if B else np.zeros(0, np.int32),
+        tok_ent=np.repeat(np.arange(B, dtype=np.int32), lens),
+        tok_pos=np.concatenate([np.arange(e.pos0, e.pos0 + n, dtype=np.int32) for e, n in zip(entries, lens)]) if B else np.zeros(0, np.int32),
+        ent_start=start, ent_slot=np.asarray([e.slot for e in entries], dtype=np.int32),
+        ent_pos0=np.asarray([e.pos0 for e in entries], dtype=np.int32), block_table=bt, want_rows=np.asarray(want, dtype=np.int32), T=T, B=B)

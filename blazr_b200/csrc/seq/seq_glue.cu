@@ -1,0 +1,308 @@
+// seq_glue.cu -- element-wise / per-row operators of layer-list models: embedding into residual streams, stream mixing fused
+// with the grouped RMS norm, short causal convolutions with carried state, gated activations, arg-max.  All arithmetic in f32.
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+
+#include "seq_common.cuh"
+
+namespace b200seq {
+
+static std::atomic<int64_t> g_launches{0};
+static thread_local char g_err[512] = "";
+void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+int cuda_status(cudaError_t e, const char* what) { return fail(B200SEQ_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e)); }
+
+__device__ int g_error_flags = 0;
+int* error_flag_dev() {
+    int* p = nullptr;
+    cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_error_flags);
+    return p;
+}
+
+constexpr int MAX_STREAMS = 8;
+constexpr int MAX_TAPS = 8;
+
+__global__ void embed_streams_kernel(const __nv_bfloat16* __restrict__ table, const int32_t* __restrict__ ids, float scale, int S, int W,
+                                     float* __restrict__ X) {
+    const int t = blockIdx.x;
+    const __nv_bfloat16* row = table + (int64_t)ids[t] * W;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+        const float v = __bfloat162float(row[i]) * scale;
+        for (int s = 0; s < S; ++s) X[((int64_t)t * S + s) * W + i] = v;
+    }
+}
+
+// one block per row; dynamic shared memory: W floats (the collapsed vector) + 40 floats of reduction scratch
+__global__ void hc_norm_kernel(float* __restrict__ X, const float* __restrict__ y, const float* __restrict__ post, const float* __restrict__ in_w,
+                               const float* __restrict__ norm_w, int S, int W, int groups, float eps, const int32_t* __restrict__ rows,
+                               void* __restrict__ out, int out_dtype) {
+    extern __shared__ float sm[];
+    float* u = sm;
+    float* red = sm + W;
+    const int r = blockIdx.x;
+    const int64_t t = rows ? rows[r] : r;
+    float mixr[MAX_STREAMS * MAX_STREAMS], outr[MAX_STREAMS], inr[MAX_STREAMS];
+    if (y) {
+        for (int s = 0; s < S; ++s) outr[s] = post[s];
+        for (int s = 0; s < S * S; ++s) mixr[s] = post[S + s];
+    }
+    if (norm_w)
+        for (int s = 0; s < S; ++s) inr[s] = in_w[s];
+    float* Xt = X + t * S * W;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+        float xs[MAX_STREAMS];
+        for (int s = 0; s < S; ++s) xs[s] = Xt[(int64_t)s * W + i];
+        if (y) {
+            const float yv = y[t * W + i];
+            float xn[MAX_STREAMS];
+            for (int j = 0; j < S; ++j) {
+                float a = 0.f;
+                for (int s = 0; s < S; ++s) a = fmaf(mixr[s * S + j], xs[s], a);
+                xn[j] = fmaf(outr[j], yv, a);
+            }
+            for (int j = 0; j < S; ++j) {
+                xs[j] = xn[j];
+                Xt[(int64_t)j * W + i] = xn[j];
+            }
+        }
+        if (norm_w) {
+            float a = 0.f;
+            for (int s = 0; s < S; ++s) a = fmaf(inr[s], xs[s], a);
+            u[i] = a;
+        }
+    }
+    if (!norm_w) return;
+    __syncthreads();
+    const int Wg = W / groups;
+    for (int g = 0; g < groups; ++g) {
+        float ss = 0.f;
+        for (int i = threadIdx.x; i < Wg; i += blockDim.x) {
+            const float v = u[g * Wg + i];
+            ss = fmaf(v, v, ss);
+        }
+        ss = block_sum(ss, red);
+        const float rinv = 1.0f / sqrtf(ss / (float)Wg + eps);
+        for (int i = threadIdx.x; i < Wg; i += blockDim.x) store_act(out, out_dtype, (int64_t)r * W + g * Wg + i, u[g * Wg + i] * rinv * norm_w[g * Wg + i]);
+    }
+}
+
+// thread = one channel, blockIdx.y = a tile of CONV_TILE consecutive token rows.  The first taps-1 tokens of an entry read the carried
+// state; they and the state's rewrite belong to the thread that meets the entry's first token, so no other thread touches that state.
+constexpr int CONV_TILE = 16;
+__global__ void causal_conv_kernel(const float* __restrict__ x, int64_t ldx, const float* __restrict__ w, const float* __restrict__ bias,
+                                   float* __restrict__ state, b200seq_step st, int C, int taps, int mode, void* __restrict__ out, int out_dtype,
+                                   int64_t ldo) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    float wr[MAX_TAPS];
+#pragma unroll
+    for (int j = 0; j < MAX_TAPS; ++j) wr[j] = j < taps ? w[(int64_t)c * taps + j] : 0.f;
+    const float b = bias ? bias[c] : 0.f;
+    const int hist = taps - 1;
+    auto emit = [&](int64_t row, float acc, float xin) {
+        float v = acc + b;
+        if (mode & B200SEQ_CONV_SILU) v = siluf_acc(v);
+        if (mode & B200SEQ_CONV_RESIDUAL) v = xin + v;
+        store_act(out, out_dtype, row * ldo + c, v);
+    };
+    const int t0 = blockIdx.y * CONV_TILE, t1 = min(t0 + CONV_TILE, st.T);
+    for (int t = t0; t < t1; ++t) {
+        const int e = st.tok_ent[t];
+        const int s0 = st.ent_start[e];
+        const int i = t - s0;
+        if (i < hist) {
+            if (i != 0) continue;
+            const int len = st.ent_start[e + 1] - s0;
+            const int64_t sbase = (int64_t)st.ent_slot[e] * hist * C + c;
+            const bool fresh = st.ent_pos0[e] == 0;
+            float old[MAX_TAPS];
+#pragma unroll
+            for (int j = 0; j < MAX_TAPS; ++j) old[j] = (j < hist && !fresh) ? state[sbase + (int64_t)j * C] : 0.f;
+            // input at entry-relative index idx (negative = carried)
+            auto src = [&](int idx) -> float {
+                if (idx >= 0) return x[(int64_t)(s0 + idx) * ldx + c];
+                float v = 0.f;
+#pragma unroll
+                for (int j = 0; j < MAX_TAPS; ++j)
+                    if (j == hist + idx) v = old[j];
+                return v;
+            };
+            const int n_own = min(hist, len);
+            for (int ii = 0; ii < n_own; ++ii) {
+                float acc = 0.f;
+                for (int j = 0; j < taps; ++j) acc = fmaf(wr[j], src(ii - hist + j), acc);
+                emit(s0 + ii, acc, x[(int64_t)(s0 + ii) * ldx + c]);
+            }
+            float nv[MAX_TAPS];
+#pragma unroll
+            for (int j = 0; j < MAX_TAPS; ++j) nv[j] = j < hist ? src(len - hist + j) : 0.f;
+#pragma unroll
+            for (int j = 0; j < MAX_TAPS; ++j)
+                if (j < hist) state[sbase + (int64_t)j * C] = nv[j];
+            continue;
+        }
+        float acc = 0.f;
+#pragma unroll
+        for (int j = 0; j < MAX_TAPS; ++j)
+            if (j < taps) acc = fmaf(wr[j], x[(int64_t)(t - hist + j) * ldx + c], acc);
+        emit(t, acc, x[(int64_t)t * ldx + c]);
+    }
+}
+
+__global__ void group_rmsnorm_kernel(const float* __restrict__ x, int64_t ldx, const float* __restrict__ w, int D, int groups, float eps,
+                                     void* __restrict__ out, int out_dtype) {
+    __shared__ float red[40];
+    const int64_t t = blockIdx.x;
+    const float* xr = x + t * ldx;
+    const int Dg = D / groups;
+    for (int g = 0; g < groups; ++g) {
+        float ss = 0.f;
+        for (int i = threadIdx.x; i < Dg; i += blockDim.x) {
+            const float v = xr[g * Dg + i];
+            ss = fmaf(v, v, ss);
+        }
+        ss = block_sum(ss, red);
+        const float rinv = 1.0f / sqrtf(ss / (float)Dg + eps);
+        for (int i = threadIdx.x; i < Dg; i += blockDim.x) {
+            const int k = g * Dg + i;
+            store_act(out, out_dtype, t * D + k, xr[k] * rinv * (w ? w[k] : 1.f));
+        }
+    }
+}
+
+__global__ void gated_act_kernel(const float* __restrict__ gu, int64_t ldg, int T, int F, float limit, float alpha, float up_shift,
+                                 void* __restrict__ out, int out_dtype) {
+    const int64_t n = (int64_t)T * F;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t t = idx / F;
+        const int f = (int)(idx - t * F);
+        const float g = fminf(gu[t * ldg + f], limit);
+        const float u = fminf(fmaxf(gu[t * ldg + F + f], -limit), limit);
+        store_act(out, out_dtype, idx, g * sigmoidf_acc(alpha * g) * (u + up_shift));
+    }
+}
+
+__global__ void argmax_kernel(const float* __restrict__ logits, int V, int32_t* __restrict__ ids) {
+    __shared__ float bv[32];
+    __shared__ int bi[32];
+    const float* row = logits + (int64_t)blockIdx.x * V;
+    float best = -INFINITY;
+    int arg = 0x7fffffff;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+        const float v = row[i];
+        if (v > best || (v == best && i < arg)) best = v, arg = i;
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, arg, o);
+        if (ov > best || (ov == best && oi < arg)) best = ov, arg = oi;
+    }
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    if (lane == 0) bv[wid] = best, bi[wid] = arg;
+    __syncthreads();
+    if (wid == 0) {
+        const int nw = blockDim.x >> 5;
+        best = lane < nw ? bv[lane] : -INFINITY;
+        arg = lane < nw ? bi[lane] : 0x7fffffff;
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, arg, o);
+            if (ov > best || (ov == best && oi < arg)) best = ov, arg = oi;
+        }
+        if (lane == 0) ids[blockIdx.x] = arg == 0x7fffffff ? 0 : arg;
+    }
+}
+
+}  // namespace b200seq
+
+using namespace b200seq;
+
+extern "C" {
+
+const char* b200seq_last_error(void) { return g_err; }
+int b200seq_version(void) { return 1; }
+int64_t b200seq_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int b200seq_error_flags(int* flags_out) {
+    if (!flags_out) return fail(B200SEQ_ERR_INVALID_ARG, "flags_out is null");
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return cuda_status(e, "synchronize");
+    int zero = 0;
+    e = cudaMemcpyFromSymbol(flags_out, g_error_flags, sizeof(int));
+    if (e != cudaSuccess) return cuda_status(e, "read error flags");
+    e = cudaMemcpyToSymbol(g_error_flags, &zero, sizeof(int));
+    if (e != cudaSuccess) return cuda_status(e, "clear error flags");
+    return 0;
+}
+
+int b200seq_embed_streams(const void* table, const int32_t* ids, float scale, int T, int S, int W, float* X, void* stream) {
+    if (!table || !ids || !X || T < 0 || S < 1 || S > MAX_STREAMS || W < 1) return fail(B200SEQ_ERR_INVALID_ARG, "embed_streams: bad arguments");
+    if (T == 0) return 0;
+    embed_streams_kernel<<<T, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)table, ids, scale, S, W, X);
+    SEQ_LAUNCH_CHECK("embed_streams");
+    return 0;
+}
+
+int b200seq_hc_norm(float* X, const float* y, const float* post, const float* in_w, const float* norm_w, int S, int W, int groups, float eps,
+                    const int32_t* rows, int R, void* out, int out_dtype, void* stream) {
+    if (!X || S < 1 || S > MAX_STREAMS || W < 1 || R < 0) return fail(B200SEQ_ERR_INVALID_ARG, "hc_norm: bad arguments");
+    if ((y && !post) || (norm_w && (!in_w || !out || groups < 1 || W % groups))) return fail(B200SEQ_ERR_INVALID_ARG, "hc_norm: missing parameters or width not divisible by groups");
+    if (R == 0) return 0;
+    const size_t smem = ((size_t)W + 40) * sizeof(float);
+    if (smem > 200 * 1024) return fail(B200SEQ_ERR_UNSUPPORTED, "hc_norm: width %d too large", W);
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(hc_norm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return cuda_status(e, "hc_norm attribute");
+    }
+    const int nt = W >= 1024 ? 512 : (W >= 256 ? 256 : 128);
+    hc_norm_kernel<<<R, nt, smem, (cudaStream_t)stream>>>(X, y, post, in_w, norm_w, S, W, groups, eps, rows, out, out_dtype);
+    SEQ_LAUNCH_CHECK("hc_norm");
+    return 0;
+}
+
+int b200seq_causal_conv(const float* x, int64_t ldx, const float* w, const float* bias, float* state, const b200seq_step* st, int C, int taps, int mode,
+                        void* out, int out_dtype, int64_t ldo, void* stream) {
+    if (!x || !w || !st || !out || C < 1 || taps < 1 || taps > MAX_TAPS || (taps > 1 && !state)) return fail(B200SEQ_ERR_INVALID_ARG, "causal_conv: bad arguments (1 <= taps <= %d)", MAX_TAPS);
+    if (out_dtype != B200SEQ_F32 && out_dtype != B200SEQ_BF16) return fail(B200SEQ_ERR_INVALID_ARG, "causal_conv: output dtype");
+    if (st->T == 0) return 0;
+    dim3 grid((C + 127) / 128, (st->T + CONV_TILE - 1) / CONV_TILE);
+    causal_conv_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(x, ldx, w, bias, state, *st, C, taps, mode, out, out_dtype, ldo);
+    SEQ_LAUNCH_CHECK("causal_conv");
+    return 0;
+}
+
+int b200seq_group_rmsnorm(const float* x, int64_t ldx, const float* w, int T, int D, int groups, float eps, void* out, int out_dtype, void* stream) {
+    if (!x || !out || T < 0 || D < 1 || groups < 1 || D % groups) return fail(B200SEQ_ERR_INVALID_ARG, "group_rmsnorm: bad arguments");
+    if (T == 0) return 0;
+    group_rmsnorm_kernel<<<T, D / groups >= 512 ? 256 : 128, 0, (cudaStream_t)stream>>>(x, ldx, w, D, groups, eps, out, out_dtype);
+    SEQ_LAUNCH_CHECK("group_rmsnorm");
+    return 0;
+}
+
+int b200seq_gated_act(const float* gu, int64_t ldg, int T, int F, float limit, float alpha, float up_shift, void* out, int out_dtype, void* stream) {
+    if (!gu || !out || T < 0 || F < 1) return fail(B200SEQ_ERR_INVALID_ARG, "gated_act: bad arguments");
+    if (T == 0) return 0;
+    const int64_t n = (int64_t)T * F;
+    const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+    gated_act_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(gu, ldg, T, F, limit, alpha, up_shift, out, out_dtype);
+    SEQ_LAUNCH_CHECK("gated_act");
+    return 0;
+}
+
+int b200seq_argmax(const float* logits, int R, int V, int32_t* ids, void* stream) {
+    if (!logits || !ids || R < 0 || V < 1) return fail(B200SEQ_ERR_INVALID_ARG, "argmax: bad arguments");
+    if (R == 0) return 0;
+    argmax_kernel<<<R, 256, 0, (cudaStream_t)stream>>>(logits, V, ids);
+    SEQ_LAUNCH_CHECK("argmax");
+    return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,181 @@
+"""Python harness over the C ABI of libb200seq.so (include/b200seq.h): dense bfloat16-weight linear layers and the sequence
+operators of layer-list models (stream mixing + grouped RMS norm, carried-state causal convolutions, chunk / window attention
+over a paged KV pool, the state-space recurrence, gated activations, arg-max).
+
+Like blazr_b200/ops.py, PyTorch is plumbing only (device memory, streams); every compute call goes through ctypes.  The library
+is compiled on first use when it is missing (`ensure_built`): a fresh checkout needs nothing but nvcc.  There is no CPU
+fallback: without the library or without an sm_100 GPU the calls raise.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import fcntl
+import os
+import shutil
+import subprocess
+from typing import Optional
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+SRC_DIR = os.path.join(_HERE, "csrc", "seq")
+LIB_PATH = os.environ.get("B200SEQ_LIB") or os.path.join(_HERE, "lib", "libb200seq.so")
+
+F32, BF16 = 0, 2
+CONV_RESIDUAL, CONV_SILU = 1, 2
+PATH_AUTO, PATH_ROWS, PATH_TILED, PATH_TC = 0, 1, 2, 3
+_DT = {torch.float32: F32, torch.bfloat16: BF16}
+
+EXPORTS = ["b200seq_last_error", "b200seq_version", "b200seq_launch_count", "b200seq_error_flags", "b200seq_embed_streams", "b200seq_hc_norm",
+           "b200seq_causal_conv", "b200seq_group_rmsnorm", "b200seq_gated_act", "b200seq_linear", "b200seq_attn_prep", "b200seq_attn",
+           "b200seq_ssm_scan", "b200seq_argmax"]
+
+
+class SeqError(RuntimeError):
+    def __init__(self, code: int, msg: str):
+        super().__init__(f"b200seq error {code}: {msg}")
+        self.code = code
+
+
+class StepDesc(C.Structure):
+    """b200seq_step: device pointers of one step's int32 arrays (see include/b200seq.h)"""
+    _fields_ = [("tok_ent", C.c_void_p), ("tok_pos", C.c_void_p), ("ent_start", C.c_void_p), ("ent_slot", C.c_void_p), ("ent_pos0", C.c_void_p),
+                ("block_table", C.c_void_p), ("T", C.c_int32), ("B", C.c_int32), ("max_blocks", C.c_int32), ("block_size", C.c_int32)]
+
+
+def _stale() -> bool:
+    if not os.path.exists(LIB_PATH):
+        return True
+    t = os.path.getmtime(LIB_PATH)
+    srcs = [os.path.join(SRC_DIR, f) for f in os.listdir(SRC_DIR) if f.endswith((".cu", ".cuh"))] + [os.path.join(_HERE, "..", "include", "b200seq.h")]
+    return any(os.path.getmtime(s) > t for s in srcs if os.path.exists(s))
+
+
+def ensure_built(force: bool = False) -> str:
+    """compile libb200seq.so (nvcc, sm_100a) if it is missing or older than its sources; safe against concurrent callers"""
+    if "B200SEQ_LIB" in os.environ or not (force or _stale()):
+        return LIB_PATH
+    os.makedirs(os.path.dirname(LIB_PATH), exist_ok=True)
+    with open(os.path.join(os.path.dirname(LIB_PATH), ".seq_build.lock"), "w") as lk:
+        fcntl.flock(lk, fcntl.LOCK_EX)
+        if force or _stale():
+            env = dict(os.environ)
+            if "NVCC" not in env and shutil.which("nvcc") is None:
+                for cand in (os.path.join(env.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc"), "/usr/local/cuda/bin/nvcc"):
+                    if os.path.exists(cand):
+                        env["NVCC"] = cand
+                        break
+            r = subprocess.run(["make", "-C", SRC_DIR, "-j8"], capture_output=True, text=True, env=env)
+            if r.returncode != 0:
+                raise SeqError(-3, "libb200seq build failed:\n" + r.stdout[-3000:] + r.stderr[-3000:])
+    return LIB_PATH
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        ensure_built()
+        L = C.CDLL(LIB_PATH)
+        L.b200seq_last_error.restype = C.c_char_p
+        L.b200seq_launch_count.restype = C.c_int64
+        _lib = L
+    return _lib
+
+
+def _check(rc: int):
+    if rc != 0:
+        raise SeqError(rc, lib().b200seq_last_error().decode())
+
+
+def _st(t: torch.Tensor) -> C.c_void_p:
+    return C.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def _p(t: Optional[torch.Tensor]):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def launch_count() -> int:
+    return int(lib().b200seq_launch_count())
+
+
+def error_flags() -> int:
+    f = C.c_int(0)
+    _check(lib().b200seq_error_flags(C.byref(f)))
+    return f.value
+
+
+def _rows2d(t: torch.Tensor):
+    assert t.dim() == 2 and t.stride(1) == 1, "row-major 2-D view expected"
+    return t.shape[0], t.shape[1], t.stride(0)
+
+
+# ---- operators (all arguments are device tensors; outputs are written in place) --------------------------------------------
+def embed_streams(table: torch.Tensor, ids: torch.Tensor, scale: float, X: torch.Tensor):
+    T, S, W = X.shape
+    _check(lib().b200seq_embed_streams(_p(table), _p(ids), C.c_float(scale), T, S, W, _p(X), _st(X)))
+
+
+def hc_norm(X: torch.Tensor, y: Optional[torch.Tensor], post: Optional[torch.Tensor], in_w: Optional[torch.Tensor], norm_w: Optional[torch.Tensor],
+            groups: int, eps: float, out: Optional[torch.Tensor], rows: Optional[torch.Tensor] = None):
+    T, S, W = X.shape
+    R = T if rows is None else rows.numel()
+    _check(lib().b200seq_hc_norm(_p(X), _p(y), _p(post), _p(in_w), _p(norm_w), S, W, groups, C.c_float(eps), _p(rows), R, _p(out), _DT[out.dtype] if out is not None else F32, _st(X)))
+
+
+def causal_conv(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], state: Optional[torch.Tensor], step: "StepDesc", mode: int, out: torch.Tensor):
+    T, Cn, ldx = _rows2d(x)
+    _, _, ldo = _rows2d(out)
+    _check(lib().b200seq_causal_conv(_p(x), C.c_int64(ldx), _p(w), _p(bias), _p(state), C.byref(step), Cn, w.shape[1], mode, _p(out), _DT[out.dtype],
+                                     C.c_int64(ldo), _st(x)))
+
+
+def group_rmsnorm(x: torch.Tensor, w: Optional[torch.Tensor], groups: int, eps: float, out: torch.Tensor):
+    T, D, ldx = _rows2d(x)
+    assert out.is_contiguous()
+    _check(lib().b200seq_group_rmsnorm(_p(x), C.c_int64(ldx), _p(w), T, D, groups, C.c_float(eps), _p(out), _DT[out.dtype], _st(x)))
+
+
+def gated_act(gu: torch.Tensor, limit: float, alpha: float, up_shift: float, out: torch.Tensor):
+    T, F2, ldg = _rows2d(gu)
+    assert out.is_contiguous() and out.shape[1] * 2 == F2
+    _check(lib().b200seq_gated_act(_p(gu), C.c_int64(ldg), T, F2 // 2, C.c_float(limit), C.c_float(alpha), C.c_float(up_shift), _p(out), _DT[out.dtype], _st(gu)))
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, path: int = PATH_AUTO):
+    """y[M, N] (f32) = x[M, K] . w[N, K]^T; w bf16 contiguous"""
+    M, K, ldx = _rows2d(x)
+    _, N, ldy = _rows2d(y)
+    assert w.dtype == torch.bfloat16 and w.is_contiguous() and tuple(w.shape) == (N, K) and y.dtype == torch.float32 and y.shape[0] == M
+    _check(lib().b200seq_linear(_p(x), _DT[x.dtype], C.c_int64(ldx), _p(w), M, N, K, _p(y), C.c_int64(ldy), path, _st(x)))
+
+
+def attn_prep(qkvg: torch.Tensor, step: "StepDesc", kpool: torch.Tensor, vpool: torch.Tensor, H: int, G: int, D: int, V: int, qk_eps: float):
+    _, _, ld = _rows2d(qkvg)
+    _check(lib().b200seq_attn_prep(_p(qkvg), C.c_int64(ld), C.byref(step), _p(kpool), _p(vpool), H, G, D, V, C.c_float(qk_eps), _st(qkvg)))
+
+
+def attn(qkvg: torch.Tensor, step: "StepDesc", kpool: torch.Tensor, vpool: torch.Tensor, H: int, G: int, D: int, V: int, scale: float, chunk: int,
+         window: int, gated: bool, out: torch.Tensor):
+    _, _, ld = _rows2d(qkvg)
+    assert out.is_contiguous()
+    _check(lib().b200seq_attn(_p(qkvg), C.c_int64(ld), C.byref(step), _p(kpool), _p(vpool), H, G, D, V, C.c_float(scale), chunk, window, int(gated),
+                              _p(out), _DT[out.dtype], _st(qkvg)))
+
+
+def ssm_scan(proj: torch.Tensor, z0: int, dt0: int, xbc: torch.Tensor, A_log: torch.Tensor, Dp: torch.Tensor, dt_bias: torch.Tensor, state: torch.Tensor,
+             step: "StepDesc", H: int, V: int, N: int, G: int, out: torch.Tensor):
+    _, _, ldp = _rows2d(proj)
+    _, _, ldx = _rows2d(xbc)
+    assert out.is_contiguous()
+    _check(lib().b200seq_ssm_scan(_p(proj), C.c_int64(ldp), z0, dt0, _p(xbc), C.c_int64(ldx), _p(A_log), _p(Dp), _p(dt_bias), _p(state), C.byref(step),
+                                  H, V, N, G, _p(out), _st(proj)))
+
+
+def argmax(logits: torch.Tensor, ids: torch.Tensor):
+    R, V = logits.shape
+    assert logits.is_contiguous() and ids.dtype == torch.int32
+    _check(lib().b200seq_argmax(_p(logits), R, V, _p(ids), _st(logits)))
