@@ -44,6 +44,42 @@ def softplus(x):
     return torch.where(x > 30, x, torch.log1p(torch.exp(torch.clamp(x, max=30))))
 
 
+def ssm_recurrence(x, B, Cm, dt_raw, dt_bias, A_log, D, S0=None, return_state=False):
+    """x [T, H, V], B and Cm [T, G, N], dt_raw [T, H]: S_t = exp(-exp(A_log) dt) S_(t-1) + dt B_t x_t^T;  y_t = S_t^T C_t + D x_t"""
+    T, H, V = x.shape
+    G, N = B.shape[1], B.shape[2]
+    dt = softplus(dt_raw + dt_bias)
+    A = torch.exp(A_log)
+    S = torch.zeros(H, N, V, dtype=x.dtype) if S0 is None else S0.clone()
+    y = torch.zeros(T, H, V, dtype=x.dtype)
+    per = H // G
+    for t in range(T):
+        for hh in range(H):
+            g = hh // per
+            S[hh] = torch.exp(-A[hh] * dt[t, hh]) * S[hh] + dt[t, hh] * torch.outer(B[t, g], x[t, hh])
+            y[t, hh] = S[hh].T @ Cm[t, g] + D[hh] * x[t, hh]
+    return (y, S) if return_state else y
+
+
+def masked_attention(q, k, v, scale, chunk=0, window=0, gate=None):
+    """q [T, H, D], k [T, G, D], v [T, G, V]; query i sees key j <= i of its own chunk (chunk > 0) and with i - j < window (window > 0)"""
+    T, H, _ = q.shape
+    G = k.shape[1]
+    out = torch.zeros(T, H, v.shape[2], dtype=q.dtype)
+    per = H // G
+    for i in range(T):
+        lo = (i // chunk) * chunk if chunk > 0 else 0
+        if window > 0:
+            lo = max(lo, i - window + 1)
+        for hh in range(H):
+            g = hh // per
+            p = torch.softmax((k[lo:i + 1, g] @ q[i, hh]) * scale, 0)
+            out[i, hh] = (p[:, None] * v[lo:i + 1, g]).sum(0)
+            if gate is not None:
+                out[i, hh] = out[i, hh] * gate[i, hh]
+    return out
+
+
 def mamba2(h: torch.Tensor, P: Dict[str, torch.Tensor], pre: str, m: dict, eps: float) -> torch.Tensor:
     """state-space mixer; m: heads, vdim, state, groups, norm_groups, conv"""
     T = h.shape[0]
@@ -55,16 +91,7 @@ def mamba2(h: torch.Tensor, P: Dict[str, torch.Tensor], pre: str, m: dict, eps: 
     x = xbc[:, :inner].reshape(T, H, V)
     B = xbc[:, inner:inner + G * N].reshape(T, G, N)
     Cm = xbc[:, inner + G * N:].reshape(T, G, N)
-    dt = softplus(dt + P[pre + "dt_bias"])
-    A = torch.exp(P[pre + "A_log"])
-    S = torch.zeros(H, N, V, dtype=h.dtype)
-    y = torch.zeros(T, H, V, dtype=h.dtype)
-    per = H // G
-    for t in range(T):
-        for hh in range(H):
-            g = hh // per
-            S[hh] = torch.exp(-A[hh] * dt[t, hh]) * S[hh] + dt[t, hh] * torch.outer(B[t, g], x[t, hh])
-            y[t, hh] = S[hh].T @ Cm[t, g] + P[pre + "D"][hh] * x[t, hh]
+    y = ssm_recurrence(x, B, Cm, dt, P[pre + "dt_bias"], P[pre + "A_log"], P[pre + "D"])
     y = y.reshape(T, inner) * silu(z)
     y = group_rms(y, m["norm_groups"], eps, P[pre + "norm"])
     return y @ P[pre + "o"].T
@@ -79,15 +106,7 @@ def chunk_attention(h: torch.Tensor, P: Dict[str, torch.Tensor], pre: str, m: di
     k = group_rms((h @ P[pre + "k"].T).reshape(T, G, D), 1, eps)
     v = (h @ P[pre + "v"].T).reshape(T, G, V)
     gate = torch.sigmoid(h @ P[pre + "g"].T)             # [T, H]
-    out = torch.zeros(T, H, V, dtype=h.dtype)
-    per = H // G
-    for i in range(T):
-        lo = (i // cs) * cs
-        for hh in range(H):
-            g = hh // per
-            s = (k[lo:i + 1, g] @ q[i, hh]) * m["scale"]
-            p = torch.softmax(s, 0)
-            out[i, hh] = (p[:, None] * v[lo:i + 1, g]).sum(0) * gate[i, hh]
+    out = masked_attention(q, k, v, m["scale"], chunk=cs, gate=gate)
     return out.reshape(T, H * V) @ P[pre + "o"].T
 
 
@@ -165,7 +184,7 @@ def random_model(cfg: dict, seed: int = 0) -> Dict[str, torch.Tensor]:
             P[f"l{i}.mlp.gate"] = r(ff, W, sc=W ** -0.5)
             P[f"l{i}.mlp.up"] = r(ff, W, sc=W ** -0.5)
             P[f"l{i}.mlp.down"] = r(W, ff, sc=ff ** -0.5)
-    return P
+    return {k: v.bfloat16().float() for k, v in P.items()}
 
 
 def write_checkpoint(folder: str, cfg: dict, P: Dict[str, torch.Tensor]) -> None:

@@ -1,0 +1,310 @@
+"""libb200seq operators, each alone, against the plain float64 restatement in tests/seq_oracle.py.
+
+Every sequence operator is run over a flat mixed batch (several entries, portions that continue earlier ones, scattered pages and
+slots) and must give, for each sequence, what the whole sequence gives in one piece."""
+import numpy as np
+import pytest
+import torch
+
+import seq_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def ops():
+    if not torch.cuda.is_available():
+        pytest.skip("no GPU")
+    from blazr_b200 import seqops
+    seqops.lib()
+    return seqops
+
+
+def dev_step(ops, entries, block_size):
+    """entries: [(n_tokens, pos0, slot, block_table)] -> (StepDesc, keep-alive tensors)"""
+    from blazr_b200.batch import StepEntry, build_step
+    sa = build_step([StepEntry([0] * n, p0, slot, bt) for n, p0, slot, bt in entries], block_size)
+    t = {k: torch.from_numpy(np.ascontiguousarray(getattr(sa, k))).to(DEV) for k in ("tok_ent", "tok_pos", "ent_start", "ent_slot", "ent_pos0", "block_table")}
+    d = ops.StepDesc(t["tok_ent"].data_ptr(), t["tok_pos"].data_ptr(), t["ent_start"].data_ptr(), t["ent_slot"].data_ptr(), t["ent_pos0"].data_ptr(),
+                     t["block_table"].data_ptr(), sa.T, sa.B, sa.block_table.shape[1], block_size)
+    return d, t
+
+
+def close(got, ref, tol):
+    ref = ref.double()
+    err = (got.double().cpu() - ref).abs().max().item() / max(ref.abs().max().item(), 1e-30)
+    assert err < tol, f"relative error {err:.3e} >= {tol}"
+
+
+def rnd(*shape, seed=0, scale=1.0):
+    return torch.randn(*shape, generator=torch.Generator().manual_seed(seed)) * scale
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 37, 40), (3, 64, 96), (7, 130, 200), (9, 61, 33), (70, 130, 72), (200, 257, 136)])
+@pytest.mark.parametrize("xdt", [torch.float32, torch.bfloat16])
+def test_linear_paths(ops, M, N, K, xdt):
+    x = rnd(M, K, seed=1).to(xdt)
+    w = rnd(N, K, seed=2, scale=K ** -0.5).bfloat16()
+    ref = x.double() @ w.double().T
+    for path in (ops.PATH_ROWS, ops.PATH_TILED, ops.PATH_AUTO):
+        y = torch.full((M, N + 3), 7.0, device=DEV)
+        ops.linear(x.to(DEV), w.to(DEV), y[:, :N], path)
+        close(y[:, :N], ref, 5e-6)
+        assert bool((y[:, N:] == 7.0).all())
+
+
+def test_linear_row_does_not_depend_on_the_batch(ops):
+    x = rnd(40, 96, seed=3)
+    w = rnd(50, 96, seed=4).bfloat16().to(DEV)
+    for path in (ops.PATH_ROWS, ops.PATH_TILED):
+        full = torch.empty(40, 50, device=DEV)
+        ops.linear(x.to(DEV), w, full, path)
+        one = torch.empty(1, 50, device=DEV)
+        ops.linear(x[17:18].contiguous().to(DEV), w, one, path)
+        assert torch.equal(one[0], full[17])
+
+
+@pytest.mark.parametrize("S,W,groups", [(1, 40, 1), (3, 48, 2), (4, 30, 5), (8, 1200, 3)])
+def test_stream_mix_and_group_norm(ops, S, W, groups):
+    T, eps = 5, 1e-3
+    X, y = rnd(T, S, W, seed=5), rnd(T, W, seed=6)
+    outv, mix, inw, nw = rnd(S, seed=7), rnd(S, S, seed=8), rnd(S, seed=9), rnd(W, seed=10)
+    Xn = torch.einsum("st,nsw->ntw", mix.double(), X.double()) + outv.double()[None, :, None] * y.double()[:, None, :]
+    u = torch.einsum("s,nsw->nw", inw.double(), Xn)
+    ref = O.group_rms(u, groups, eps, nw.double())
+    Xd = X.to(DEV).clone()
+    out = torch.empty(T, W, device=DEV)
+    ops.hc_norm(Xd, y.to(DEV), torch.cat([outv, mix.reshape(-1)]).to(DEV), inw.to(DEV), nw.to(DEV), groups, eps, out)
+    close(Xd, Xn, 1e-6)
+    close(out, ref, 1e-5)
+    # collapse only (no pending update), selected rows, bfloat16 output
+    rows = torch.tensor([3, 0], dtype=torch.int32, device=DEV)
+    out2 = torch.empty(2, W, device=DEV, dtype=torch.bfloat16)
+    ops.hc_norm(Xd, None, None, inw.to(DEV), nw.to(DEV), groups, eps, out2, rows=rows)
+    close(out2.float(), ref[[3, 0]], 1e-2)
+    g = torch.empty(T, W, device=DEV)
+    ops.group_rmsnorm(u.float().to(DEV), nw.to(DEV), groups, eps, g)
+    close(g, ref, 1e-5)
+
+
+@pytest.mark.parametrize("taps", [1, 2, 4, 7])
+@pytest.mark.parametrize("mode", ["residual", "silu"])
+def test_causal_conv_carries_its_tail(ops, taps, mode):
+    C, slots = 70, 5
+    lens = {"a": 23, "b": 9, "c": 1, "d": 12}
+    xs = {k: rnd(n, C, seed=20 + i) for i, (k, n) in enumerate(lens.items())}
+    w, b = rnd(C, taps, seed=30), rnd(C, seed=31)
+    ref = {}
+    for k, x in xs.items():
+        c = O.causal_conv(x.double(), w.double(), b.double() if mode == "silu" else None)
+        ref[k] = O.silu(c) if mode == "silu" else x.double() + c
+    state = torch.full((slots, max(taps - 1, 1), C), 99.0, device=DEV)      # stale: a fresh sequence must not read it
+    slot = {"a": 3, "b": 0, "c": 4, "d": 1}
+    fed = {k: 0 for k in lens}
+    got = {k: [] for k in lens}
+    # portions down to one token, shorter than the carried tail; entries of other sequences in between
+    plan = [[("a", 1), ("b", 2)], [("a", 2), ("c", 1), ("b", 1)], [("b", 6), ("a", 17)], [("a", 1), ("d", 12)], [("a", 2)]]
+    for step in plan:
+        ents = [(n, fed[k], slot[k], [0]) for k, n in step]
+        d, keep = dev_step(ops, ents, 4096)
+        x = torch.cat([xs[k][fed[k]:fed[k] + n] for k, n in step]).to(DEV)
+        out = torch.empty_like(x)
+        ops.causal_conv(x, w.to(DEV), b.to(DEV) if mode == "silu" else None, state, d, ops.CONV_SILU if mode == "silu" else ops.CONV_RESIDUAL, out)
+        o = 0
+        for k, n in step:
+            got[k].append(out[o:o + n].cpu())
+            o += n
+            fed[k] += n
+    for k in lens:
+        assert fed[k] == lens[k]
+        close(torch.cat(got[k]), ref[k], 1e-5)
+
+
+@pytest.mark.parametrize("F,limit", [(33, 0.7), (128, 2.0)])
+def test_gated_activation(ops, F, limit):
+    gu = rnd(6, 2 * F, seed=40, scale=2.0)
+    g = torch.clamp(gu[:, :F].double(), max=limit)
+    u = torch.clamp(gu[:, F:].double(), -limit, limit)
+    ref = g * torch.sigmoid(1.702 * g) * (u + 1)
+    out = torch.empty(6, F, device=DEV)
+    ops.gated_act(gu.to(DEV), limit, 1.702, 1.0, out)
+    close(out, ref, 1e-6)
+    assert (gu[:, :F] > limit).any() and (gu[:, F:] < -limit).any() and (gu[:, :F] < -limit).any()   # every branch of the clamps is hit
+
+
+def test_argmax_first_maximum(ops):
+    lg = rnd(4, 1000, seed=41)
+    lg[1, 77] = lg[1, 901] = 50.0
+    lg[2, 999] = 60.0
+    ids = torch.empty(4, dtype=torch.int32, device=DEV)
+    ops.argmax(lg.to(DEV), ids)
+    assert ids.tolist() == [int(lg[0].argmax()), 77, 999, int(lg[3].argmax())]
+
+
+def run_attention(ops, q, k, v, gate, scale, chunk, window, eps, plan, block_size, n_pages, act=torch.float32, seed=0):
+    """feeds sequences (dict name -> (q, k, v, gate) of whole sequences) through prep + attend as the plan says; pages are taken
+    from a shuffled list; returns name -> [T, H*V]"""
+    names = list(q)
+    H, D = q[names[0]].shape[1:]
+    G, V = v[names[0]].shape[1:]
+    kpool = torch.full((n_pages, block_size, G, D), 1e4, device=DEV)
+    vpool = torch.full((n_pages, block_size, G, V), 1e4, device=DEV)
+    free = torch.randperm(n_pages, generator=torch.Generator().manual_seed(seed)).tolist()
+    pages = {n: [] for n in names}
+    fed = {n: 0 for n in names}
+    got = {n: [] for n in names}
+    for step in plan:
+        ents = []
+        for n, cnt in step:
+            while len(pages[n]) * block_size < fed[n] + cnt:
+                pages[n].append(free.pop())
+            ents.append((cnt, fed[n], 0, pages[n]))
+        d, keep = dev_step(ops, ents, block_size)
+        rows = [torch.cat([q[n][fed[n]:fed[n] + c].reshape(c, -1), k[n][fed[n]:fed[n] + c].reshape(c, -1), v[n][fed[n]:fed[n] + c].reshape(c, -1)]
+                          + ([gate[n][fed[n]:fed[n] + c]] if gate is not None else []), 1) for n, c in step]
+        qkvg = torch.cat(rows).contiguous().to(DEV)
+        out = torch.empty(qkvg.shape[0], H * V, device=DEV, dtype=act)
+        ops.attn_prep(qkvg, d, kpool, vpool, H, G, D, V, eps)
+        ops.attn(qkvg, d, kpool, vpool, H, G, D, V, scale, chunk, window, gate is not None, out)
+        o = 0
+        for n, c in step:
+            got[n].append(out[o:o + c].float().cpu())
+            o += c
+            fed[n] += c
+        for n, c in step:            # a finished sequence gives its pages back at once: the next one gets them
+            if fed[n] == q[n].shape[0]:
+                free.extend(pages[n])
+                pages[n] = []
+    assert ops.error_flags() == 0
+    return {n: torch.cat(got[n]) for n in names}
+
+
+def attention_case(T, H, G, D, V, seed):
+    return rnd(T, H, D, seed=seed), rnd(T, G, D, seed=seed + 1), rnd(T, G, V, seed=seed + 2), rnd(T, H, seed=seed + 3)
+
+
+@pytest.mark.parametrize("H,G,D,V,chunk,window,bs", [(4, 2, 16, 8, 24, 0, 16), (3, 3, 20, 40, 7, 0, 4), (2, 1, 64, 64, 0, 0, 16), (4, 4, 8, 8, 0, 10, 8),
+                                                     (6, 2, 12, 33, 16, 5, 16)])
+def test_attention_mixed_batch_matches_whole_sequences(ops, H, G, D, V, chunk, window, bs):
+    eps, scale = 1e-4, 0.37
+    lens = {"a": 75, "b": 30, "c": 3}
+    data = {n: attention_case(T, H, G, D, V, 50 + 10 * i) for i, (n, T) in enumerate(lens.items())}
+    q, k, v, gate = ({n: d[j] for n, d in data.items()} for j in range(4))
+    ref = {}
+    for n in lens:
+        qn = O.group_rms(q[n].double(), 1, eps)
+        kn = O.group_rms(k[n].double(), 1, eps)
+        ref[n] = O.masked_attention(qn, kn, v[n].double(), scale, chunk, window, torch.sigmoid(gate[n].double())).reshape(lens[n], -1)
+    plan = [[("a", 40), ("b", 2)], [("b", 1), ("a", 1), ("c", 3)], [("a", 2), ("b", 27)], [("a", 32)]]
+    got = run_attention(ops, q, k, v, gate, scale, chunk, window, eps, plan, bs, n_pages=-(-75 // bs) + -(-30 // bs) + 2)
+    for n in lens:
+        close(got[n], ref[n], 2e-5)
+
+
+@pytest.mark.parametrize("decode", [False, True])
+def test_attention_chunk_edges_show(ops, decode):
+    """one key carries a value that stands out and a direction every later query points at: the output shows at once whether the key
+    was visible, so a chunk edge that is one position off cannot hide among many small weights"""
+    H = G = 1
+    D, V, chunk, bs, T = 16, 8, 20, 16, 70
+    hot = 39                                           # last position of the chunk [20, 40)
+    q = torch.zeros(T, H, D)
+    k = rnd(T, G, D, seed=60, scale=0.05)
+    v = rnd(T, G, V, seed=61, scale=0.1)
+    q[:, 0, 0] = 1.0
+    k[hot] = 0
+    k[hot, 0, 0] = 1.0
+    v[hot] = 100.0
+    plan = [[("a", 35)]] + [[("a", 1)]] * 35 if decode else [[("a", 38)], [("a", 2)], [("a", 30)]]
+    got = run_attention(ops, {"a": q}, {"a": k}, {"a": v}, None, 40.0, chunk, 0, -1.0, plan, bs, n_pages=6)["a"]
+    ref = O.masked_attention(q.double(), k.double(), v.double(), 40.0, chunk, 0).reshape(T, -1)
+    close(got, ref, 2e-5)
+    assert got[hot].min() > 99 and got[hot - 1].abs().max() < 5      # the key sees itself; earlier positions of its chunk do not
+    assert got[hot + 1].abs().max() < 5                                # first position of the next chunk: just outside
+
+
+def test_attention_far_key_among_hundreds_and_window_edges(ops):
+    H, G, D, V, bs, T, window = 2, 1, 32, 16, 16, 400, 128
+    q, k, v, _ = attention_case(T, H, G, D, V, 70)
+    k = k * 0.05
+    far = 16                                           # first slot of a page
+    q[:, :, :] = 0
+    q[:, :, 3] = 1.0
+    k[far] = 0
+    k[far, 0, 3] = 1.0
+    v[far] = -50.0
+    for win in (0, window):
+        plan = [[("a", 300)], [("a", 2)]] + [[("a", 1)]] * 98
+        got = run_attention(ops, {"a": q}, {"a": k}, {"a": v}, None, 30.0, 0, win, -1.0, plan, bs, n_pages=26)["a"]
+        ref = O.masked_attention(q.double(), k.double(), v.double(), 30.0, 0, win).reshape(T, -1)
+        close(got, ref, 2e-5)
+        if win:
+            assert got[far + win - 1].max() < -49 and got[far + win].abs().max() < 5    # last query that sees it, first that does not
+        else:
+            assert got[T - 1].max() < -49                                                # 383 positions back, through 24 pages
+
+
+@pytest.mark.parametrize("H,G,N,V", [(4, 2, 16, 8), (3, 1, 32, 40), (2, 2, 5, 64), (6, 3, 64, 32), (1, 1, 128, 7)])
+def test_state_space_scan_carries_state_between_portions(ops, H, G, N, V):
+    lens = {"a": 37, "b": 11, "c": 2}
+    inner = H * V
+    ld = 2 * inner + 2 * G * N + H
+    slot = {"a": 2, "b": 0, "c": 2}                 # c takes a's slot after a finished: stale state must not leak
+    data, ref = {}, {}
+    A_log, Dp, dtb = rnd(H, seed=80, scale=0.5), rnd(H, seed=81), rnd(H, seed=82)
+    for i, (n, T) in enumerate(lens.items()):
+        proj = rnd(T, ld, seed=83 + i)
+        xbc = rnd(T, inner + 2 * G * N, seed=90 + i)
+        data[n] = (proj, xbc)
+        y = O.ssm_recurrence(xbc[:, :inner].double().reshape(T, H, V), xbc[:, inner:inner + G * N].double().reshape(T, G, N),
+                             xbc[:, inner + G * N:].double().reshape(T, G, N), proj[:, ld - H:].double(), dtb.double(), A_log.double(), Dp.double())
+        ref[n] = y.reshape(T, inner) * O.silu(proj[:, :inner].double())
+    state = torch.full((3, H, N, V), 1e3, device=DEV)
+    plan = [[("a", 20), ("b", 1)], [("b", 2), ("a", 1)], [("a", 16), ("b", 8)], [("c", 2)]]
+    fed = {n: 0 for n in lens}
+    got = {n: [] for n in lens}
+    for step in plan:
+        d, keep = dev_step(ops, [(c, fed[n], slot[n], [0]) for n, c in step], 4096)
+        proj = torch.cat([data[n][0][fed[n]:fed[n] + c] for n, c in step]).to(DEV)
+        xbc = torch.cat([data[n][1][fed[n]:fed[n] + c] for n, c in step]).to(DEV)
+        out = torch.empty(proj.shape[0], inner, device=DEV)
+        ops.ssm_scan(proj, 0, ld - H, xbc, A_log.to(DEV), Dp.to(DEV), dtb.to(DEV), state, d, H, V, N, G, out)
+        o = 0
+        for n, c in step:
+            got[n].append(out[o:o + c].cpu())
+            o += c
+            fed[n] += c
+    for n in lens:
+        close(torch.cat(got[n]), ref[n], 2e-5)
+
+
+def test_state_space_long_memory_shows(ops):
+    """decay close to one and a single early input: every later output still carries it, so a state that is dropped or reset between
+    steps shows"""
+    H = G = 1
+    N, V, T = 8, 4, 120
+    inner, ld = H * V, 2 * H * V + 2 * N + H
+    proj = torch.zeros(T, ld)
+    proj[:, :inner] = 3.0                               # gate input
+    proj[:, ld - 1] = -2.0                              # small step
+    xbc = torch.zeros(T, inner + 2 * N)
+    xbc[0, :inner] = 50.0
+    xbc[0, inner:inner + N] = 1.0
+    xbc[:, inner + N:] = 1.0
+    A_log, Dp, dtb = torch.tensor([-6.0]), torch.zeros(1), torch.zeros(1)
+    y = O.ssm_recurrence(xbc[:, :inner].double().reshape(T, 1, V), xbc[:, inner:inner + N].double().reshape(T, 1, N),
+                         xbc[:, inner + N:].double().reshape(T, 1, N), proj[:, ld - 1:].double(), dtb.double(), A_log.double(), Dp.double())
+    ref = y.reshape(T, inner) * O.silu(proj[:, :inner].double())
+    state = torch.zeros((1, H, N, V), device=DEV)
+    outs, fed = [], 0
+    for c in [1, 2, 50] + [1] * 67:
+        d, keep = dev_step(ops, [(c, fed, 0, [0])], 4096)
+        out = torch.empty(c, inner, device=DEV)
+        ops.ssm_scan(proj[fed:fed + c].to(DEV), 0, ld - 1, xbc[fed:fed + c].to(DEV), A_log.to(DEV), Dp.to(DEV), dtb.to(DEV), state, d, H, V, N, G, out)
+        outs.append(out.cpu())
+        fed += c
+    got = torch.cat(outs)
+    close(got, ref, 2e-5)
+    assert got[-1].min() > 0.5 * got[0].max() > 0
