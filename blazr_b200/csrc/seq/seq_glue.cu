@@ -178,14 +178,14 @@ __global__ void group_rmsnorm_kernel(const float* __restrict__ x, int64_t ldx, c
     }
 }
 
-__global__ void gated_act_kernel(const float* __restrict__ gu, int64_t ldg, int T, int F, float limit, float alpha, float up_shift,
+__global__ void gated_act_kernel(const float* __restrict__ gu, int64_t ldg, int T, int F, float limit, float alpha, float up_shift, int interleaved,
                                  void* __restrict__ out, int out_dtype) {
     const int64_t n = (int64_t)T * F;
     for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (int64_t)gridDim.x * blockDim.x) {
         const int64_t t = idx / F;
         const int f = (int)(idx - t * F);
-        const float g = fminf(gu[t * ldg + f], limit);
-        const float u = fminf(fmaxf(gu[t * ldg + F + f], -limit), limit);
+        const float g = fminf(gu[t * ldg + (interleaved ? 2 * f : f)], limit);
+        const float u = fminf(fmaxf(gu[t * ldg + (interleaved ? 2 * f + 1 : F + f)], -limit), limit);
         store_act(out, out_dtype, idx, g * sigmoidf_acc(alpha * g) * (u + up_shift));
     }
 }
@@ -287,12 +287,13 @@ int b200seq_group_rmsnorm(const float* x, int64_t ldx, const float* w, int T, in
     return 0;
 }
 
-int b200seq_gated_act(const float* gu, int64_t ldg, int T, int F, float limit, float alpha, float up_shift, void* out, int out_dtype, void* stream) {
+int b200seq_gated_act(const float* gu, int64_t ldg, int T, int F, float limit, float alpha, float up_shift, int interleaved, void* out, int out_dtype,
+                      void* stream) {
     if (!gu || !out || T < 0 || F < 1) return fail(B200SEQ_ERR_INVALID_ARG, "gated_act: bad arguments");
     if (T == 0) return 0;
     const int64_t n = (int64_t)T * F;
     const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
-    gated_act_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(gu, ldg, T, F, limit, alpha, up_shift, out, out_dtype);
+    gated_act_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(gu, ldg, T, F, limit, alpha, up_shift, interleaved, out, out_dtype);
     SEQ_LAUNCH_CHECK("gated_act");
     return 0;
 }

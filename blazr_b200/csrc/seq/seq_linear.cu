@@ -9,6 +9,8 @@ namespace b200seq {
 
 int launch_linear_tc(const void* x_bf16, int64_t ldx, const void* w_bf16, int M, int N, int K, float* y, int64_t ldy, cudaStream_t st);
 bool linear_tc_usable(int x_dtype, int64_t ldx, int M, int N, int K, const void* x, const void* w);
+int launch_linear_tc_gated(const void* x, int64_t ldx, const void* w_interleaved, int M, int F, int K, float limit, float alpha, float shift, void* out,
+                           int out_dtype, int64_t ldo, cudaStream_t st);
 
 template <typename XT>
 __device__ __forceinline__ float ld_x(const XT* p);
@@ -186,4 +188,13 @@ extern "C" int b200seq_linear(const void* x, int x_dtype, int64_t ldx, const voi
     }
     SEQ_LAUNCH_CHECK("linear");
     return 0;
+}
+
+extern "C" int b200seq_linear_gated(const void* x, int64_t ldx, const void* w, int M, int F, int K, float limit, float alpha, float up_shift, void* out,
+                                    int out_dtype, int64_t ldo, void* stream) {
+    if (!x || !w || !out || M < 0 || F < 1 || K < 1 || ldx < K || ldo < F) return fail(B200SEQ_ERR_INVALID_ARG, "linear_gated: bad arguments");
+    if (out_dtype != B200SEQ_F32 && out_dtype != B200SEQ_BF16) return fail(B200SEQ_ERR_INVALID_ARG, "linear_gated: output dtype");
+    if (M == 0) return 0;
+    if (!linear_tc_usable(B200SEQ_BF16, ldx, M, 2 * F, K, x, w)) return fail(B200SEQ_ERR_UNSUPPORTED, "linear_gated: needs K %% 8 == 0 and 16-byte aligned rows");
+    return launch_linear_tc_gated(x, ldx, w, M, F, K, limit, alpha, up_shift, out, out_dtype, ldo, (cudaStream_t)stream);
 }

@@ -179,7 +179,8 @@ class LayeredModel:
             if ls.ff is not None:
                 L["norm2"], L["canon2"] = vec(p + "norm2"), vec(p + "canon2")
                 L["hc2_in"], L["hc2_post"] = hc(p + "hc2.")
-                L["w_gu"] = lin(p + "mlp.gate", p + "mlp.up")
+                gu = lin(p + "mlp.gate", p + "mlp.up")          # stored with alternating rows (gate j, up j): the pair meets in one warp
+                L["w_gu"] = gu.view(2, ls.ff.ff, W).transpose(0, 1).reshape(2 * ls.ff.ff, W).contiguous()
                 L["w_down"] = lin(p + "mlp.down")
                 self.max_proj = max(self.max_proj, 2 * ls.ff.ff)
                 self.max_inner = max(self.max_inner, ls.ff.ff)
@@ -337,8 +338,11 @@ class LayeredModel:
         seqops.linear(yn, L["w_o"], y)
 
     def _dense_ff(self, L, f: DenseFfSpec, ws: _Workspace, T: int, a: torch.Tensor, y: torch.Tensor) -> None:
-        gu = ws.proj[:T, :2 * f.ff]
-        seqops.linear(a, L["w_gu"], gu)
         act = ws.inner_a.view(-1)[:T * f.ff].view(T, f.ff)
-        seqops.gated_act(gu, f.limit, f.alpha, f.up_shift, act)
+        if T >= seqops.TC_MIN_ROWS and seqops.tc_usable(a, a.shape[1]):     # projection and activation in one tensor-core kernel
+            seqops.linear_gated(a, L["w_gu"], f.limit, f.alpha, f.up_shift, act)
+        else:
+            gu = ws.proj[:T, :2 * f.ff]
+            seqops.linear(a, L["w_gu"], gu)
+            seqops.gated_act(gu, f.limit, f.alpha, f.up_shift, act, interleaved=True)
         seqops.linear(act, L["w_down"], y)

@@ -24,10 +24,11 @@ LIB_PATH = os.environ.get("B200SEQ_LIB") or os.path.join(_HERE, "lib", "libb200s
 F32, BF16 = 0, 2
 CONV_RESIDUAL, CONV_SILU = 1, 2
 PATH_AUTO, PATH_ROWS, PATH_TILED, PATH_TC = 0, 1, 2, 3
+TC_MIN_ROWS = 32   # b200seq_linear's automatic choice takes the tensor-core path from this many rows
 _DT = {torch.float32: F32, torch.bfloat16: BF16}
 
 EXPORTS = ["b200seq_last_error", "b200seq_version", "b200seq_launch_count", "b200seq_error_flags", "b200seq_embed_streams", "b200seq_hc_norm",
-           "b200seq_causal_conv", "b200seq_group_rmsnorm", "b200seq_gated_act", "b200seq_linear", "b200seq_attn_prep", "b200seq_attn",
+           "b200seq_causal_conv", "b200seq_group_rmsnorm", "b200seq_gated_act", "b200seq_linear", "b200seq_linear_gated", "b200seq_attn_prep", "b200seq_attn",
            "b200seq_ssm_scan", "b200seq_argmax"]
 
 
@@ -139,10 +140,10 @@ def group_rmsnorm(x: torch.Tensor, w: Optional[torch.Tensor], groups: int, eps: 
     _check(lib().b200seq_group_rmsnorm(_p(x), C.c_int64(ldx), _p(w), T, D, groups, C.c_float(eps), _p(out), _DT[out.dtype], _st(x)))
 
 
-def gated_act(gu: torch.Tensor, limit: float, alpha: float, up_shift: float, out: torch.Tensor):
+def gated_act(gu: torch.Tensor, limit: float, alpha: float, up_shift: float, out: torch.Tensor, interleaved: bool = False):
     T, F2, ldg = _rows2d(gu)
     assert out.is_contiguous() and out.shape[1] * 2 == F2
-    _check(lib().b200seq_gated_act(_p(gu), C.c_int64(ldg), T, F2 // 2, C.c_float(limit), C.c_float(alpha), C.c_float(up_shift), _p(out), _DT[out.dtype], _st(gu)))
+    _check(lib().b200seq_gated_act(_p(gu), C.c_int64(ldg), T, F2 // 2, C.c_float(limit), C.c_float(alpha), C.c_float(up_shift), int(interleaved), _p(out), _DT[out.dtype], _st(gu)))
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, path: int = PATH_AUTO):
@@ -151,6 +152,20 @@ def linear(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, path: int = PATH_A
     _, N, ldy = _rows2d(y)
     assert w.dtype == torch.bfloat16 and w.is_contiguous() and tuple(w.shape) == (N, K) and y.dtype == torch.float32 and y.shape[0] == M
     _check(lib().b200seq_linear(_p(x), _DT[x.dtype], C.c_int64(ldx), _p(w), M, N, K, _p(y), C.c_int64(ldy), path, _st(x)))
+
+
+def linear_gated(x: torch.Tensor, w_il: torch.Tensor, limit: float, alpha: float, up_shift: float, out: torch.Tensor):
+    """out[M, F] = gated_act(x . w_il^T); w_il bf16 [2F, K] with alternating gate / up rows (tensor-core path only)"""
+    M, K, ldx = _rows2d(x)
+    _, F, ldo = _rows2d(out)
+    assert x.dtype == torch.bfloat16 and w_il.dtype == torch.bfloat16 and w_il.is_contiguous() and tuple(w_il.shape) == (2 * F, K) and out.shape[0] == M
+    _check(lib().b200seq_linear_gated(_p(x), C.c_int64(ldx), _p(w_il), M, F, K, C.c_float(limit), C.c_float(alpha), C.c_float(up_shift), _p(out),
+                                      _DT[out.dtype], C.c_int64(ldo), _st(x)))
+
+
+def tc_usable(x: torch.Tensor, K: int) -> bool:
+    """whether the tensor-core path takes this activation matrix (bf16, K % 8 == 0, rows 16-byte aligned)"""
+    return x.dtype == torch.bfloat16 and K % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
 
 
 def attn_prep(qkvg: torch.Tensor, step: "StepDesc", kpool: torch.Tensor, vpool: torch.Tensor, H: int, G: int, D: int, V: int, qk_eps: float):

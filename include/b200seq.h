@@ -86,11 +86,19 @@ int b200seq_causal_conv(const float* x, int64_t ldx, const float* w, const float
 /* out[t] = group_rms(x[t], groups, eps) * w   (x f32 [T, D] stride ldx; out act dtype [T, D]) */
 int b200seq_group_rmsnorm(const float* x, int64_t ldx, const float* w, int T, int D, int groups, float eps, void* out, int out_dtype, void* stream);
 
-/* gu: f32 [T, 2F] = gate | up.  g = min(gate, limit), u = clamp(up, -limit, limit), out = g * sigmoid(alpha * g) * (u + up_shift) */
-int b200seq_gated_act(const float* gu, int64_t ldg, int T, int F, float limit, float alpha, float up_shift, void* out, int out_dtype, void* stream);
+/* gu: f32 [T, 2F] = gate | up (interleaved = 0) or gate 0, up 0, gate 1, up 1, ... (interleaved = 1).
+ * g = min(gate, limit), u = clamp(up, -limit, limit), out = g * sigmoid(alpha * g) * (u + up_shift) */
+int b200seq_gated_act(const float* gu, int64_t ldg, int T, int F, float limit, float alpha, float up_shift, int interleaved, void* out, int out_dtype,
+                      void* stream);
 
 /* y[M, N] (f32, stride ldy) = x[M, K] (f32 or bf16, stride ldx) . w[N, K]^T (bf16, contiguous) */
 int b200seq_linear(const void* x, int x_dtype, int64_t ldx, const void* w_bf16, int M, int N, int K, float* y, int64_t ldy, int path, void* stream);
+
+/* Fused gate|up projection + gated activation on the tensor-core path: w_il is the stacked weight [2F, K] with rows alternating
+ * (gate 0, up 0, gate 1, up 1, ...); out[M, F] (act dtype, stride ldo) = gated_act(x . w_il^T) with the formula of b200seq_gated_act.
+ * The [M, 2F] product is never written.  Needs bf16 activations, K % 8 == 0 and 16-byte aligned rows (B200SEQ_ERR_UNSUPPORTED otherwise). */
+int b200seq_linear_gated(const void* x_bf16, int64_t ldx, const void* w_il_bf16, int M, int F, int K, float limit, float alpha, float up_shift, void* out,
+                         int out_dtype, int64_t ldo, void* stream);
 
 /* Attention over a paged f32 KV pool (kpool [blocks][block_size][G][D], vpool [..][G][V]).
  * qkvg: f32 [T, ld] = q (H*D) | k (G*D) | v (G*V) | gate (H, only if gated).

@@ -55,6 +55,44 @@ def test_linear_paths(ops, M, N, K, xdt):
         assert bool((y[:, N:] == 7.0).all())
 
 
+@pytest.mark.parametrize("M,N,K", [(32, 128, 64), (70, 130, 72), (200, 257, 136), (129, 61, 8), (300, 448, 520), (1000, 96, 200)])
+def test_linear_tensor_core_path(ops, M, N, K):
+    x = rnd(M, K + 8, seed=11).bfloat16()[:, :K]                 # rows with a stride that is not K
+    w = rnd(N, K, seed=12, scale=K ** -0.5).bfloat16()
+    ref = x.double() @ w.double().T
+    y = torch.full((M, N + 1), 7.0, device=DEV)
+    ops.linear(x.to(DEV), w.to(DEV), y[:, :N], ops.PATH_TC)
+    close(y[:, :N], ref, 5e-6)
+    assert bool((y[:, N:] == 7.0).all()) and ops.error_flags() == 0
+    auto = torch.empty(M, N, device=DEV)
+    ops.linear(x.to(DEV), w.to(DEV), auto)                        # the automatic choice takes this path from 32 rows
+    assert torch.equal(auto, y[:, :N])
+    one = torch.empty(32, N, device=DEV)                          # a row's result does not depend on the rows beside it
+    ops.linear(x[M - 32:].to(DEV), w.to(DEV), one, ops.PATH_TC)
+    assert torch.equal(one, y[M - 32:, :N])
+
+
+@pytest.mark.parametrize("M,F,K,limit", [(33, 40, 48, 1.5), (260, 129, 200, 0.6), (128, 64, 64, 7.0)])
+@pytest.mark.parametrize("odt", [torch.float32, torch.bfloat16])
+def test_gate_up_projection_fused_with_its_activation(ops, M, F, K, limit, odt):
+    x = rnd(M, K, seed=13, scale=2.0).bfloat16()
+    wg, wu = rnd(F, K, seed=14, scale=K ** -0.5).bfloat16(), rnd(F, K, seed=15, scale=K ** -0.5).bfloat16()
+    g = torch.clamp(x.double() @ wg.double().T, max=limit)
+    u = torch.clamp(x.double() @ wu.double().T, -limit, limit)
+    ref = g * torch.sigmoid(1.702 * g) * (u + 1)
+    w_il = torch.stack([wg, wu], 1).reshape(2 * F, K).contiguous()
+    out = torch.full((M, F + 2), 3.0, device=DEV, dtype=odt)
+    ops.linear_gated(x.to(DEV), w_il.to(DEV), limit, 1.702, 1.0, out[:, :F])
+    close(out[:, :F].float(), ref, 1e-5 if odt == torch.float32 else 1e-2)
+    assert bool((out[:, F:] == 3.0).all()) and ops.error_flags() == 0
+    # the unfused pair of kernels on the same interleaved weight gives the same numbers
+    gu = torch.empty(M, 2 * F, device=DEV)
+    ops.linear(x.to(DEV), w_il.to(DEV), gu, ops.PATH_TC)
+    two = torch.empty(M, F, device=DEV, dtype=odt)
+    ops.gated_act(gu, limit, 1.702, 1.0, two, interleaved=True)
+    assert torch.equal(two, out[:, :F])
+
+
 def test_linear_row_does_not_depend_on_the_batch(ops):
     x = rnd(40, 96, seed=3)
     w = rnd(50, 96, seed=4).bfloat16().to(DEV)
