@@ -41,6 +41,11 @@ def parse_args():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--prompt", type=int, default=32, help="prompt tokens fed before the timed region (reference bench.rs:24)")
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary measurements (prefill GEMM, batch-32)")
+    ap.add_argument("--layered", default=None, metavar="DESIGN", help="instead of the default workload: prefill / decode throughput and the per-kernel "
+                    "roofline table of a layer-list design (fenorax) at real-model layer sizes, beside the dense decoder of equal size (1 GPU)")
+    ap.add_argument("--layered-sizes", default="w1024,w2048,w4096", help="comma list of blazr_b200.layered_bench.SIZES keys")
+    ap.add_argument("--layered-prompt", type=int, default=4096)
+    ap.add_argument("--layered-context", type=int, default=1024)
     return ap.parse_args()
 
 
@@ -612,9 +617,26 @@ def extras(client, cfg, scheme, pk, args):
     return out
 
 
+def run_layered(args):
+    import torch
+
+    from blazr_b200 import layered_bench
+    torch.cuda.set_device(0)
+    pk, pk_kind = peaks()
+    sampler = ClockSampler(0)
+    sampler.start()
+    res = layered_bench.run(args.layered, [s for s in args.layered_sizes.split(",") if s], pk, pk_kind, S=args.layered_prompt, ctx=args.layered_context,
+                            steps=max(8, min(args.steps, 64)))
+    res["clocks"] = sampler.stop()
+    res["impl"] = "b200"
+    print(json.dumps(res), flush=True)
+
+
 def main():
     args = parse_args()
-    if args.impl == "reference":
+    if args.layered:
+        run_layered(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_b200(args)

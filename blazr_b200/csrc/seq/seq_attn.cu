@@ -1,8 +1,9 @@
 // seq_attn.cu -- attention of a flat mixed batch (prompt portions beside single decoded tokens) over a paged f32 KV pool.
 //   prep  : per-head unit-RMS q and k (no weight), k and v rows stored at the token's page slot.
-//   attend: one block per (token, query head); the visible keys are the token's own chunk and / or window, read through the
-//           entry's block table; scores, soft-max and the weighted sum in f32; optional per-head sigmoid gate on the output.
-// A block's result depends on the token's position and on its sequence's pages only, never on the rest of the batch.
+//   attend: tiles of (token, query head) rows against tiles of the keys they can see (the token's own chunk and / or window, read
+//           through the entry's block table); scores, soft-max and the weighted sum in f32; optional per-head sigmoid gate.
+// A row's result depends on the token's position and on its sequence's pages only; the rest of the batch changes at most how the
+// keys are split among blocks (rounding).
 #include "seq_common.cuh"
 
 namespace b200seq {
@@ -49,92 +50,285 @@ __global__ void attn_prep_kernel(float* __restrict__ qkvg, int64_t ld, b200seq_s
     }
 }
 
-constexpr int ATT_WARPS = 4;
-constexpr int ATT_VR = 8;   // value elements per lane: V <= 256
-// dynamic shared memory: q[D] | per warp: m, l, acc[V]
-__global__ void __launch_bounds__(ATT_WARPS * 32) attn_kernel(const float* __restrict__ qkvg, int64_t ld, b200seq_step st, const float* __restrict__ kpool,
-                                                              const float* __restrict__ vpool, int H, int G, int D, int V, float scale, int chunk,
-                                                              int window, int gated, void* __restrict__ out, int out_dtype, int* err) {
-    extern __shared__ float sm[];
-    float* qs = sm;
-    float* wm = sm + D;                 // [ATT_WARPS]
-    float* wl = wm + ATT_WARPS;         // [ATT_WARPS]
-    float* wacc = wl + ATT_WARPS;       // [ATT_WARPS][V]
-    const int t = blockIdx.x, h = blockIdx.y;
-    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-    const int e = st.tok_ent[t], pos = st.tok_pos[t];
-    const int g = h / (H / G);
-    const float* qp = qkvg + (int64_t)t * ld + (int64_t)h * D;
-    for (int d = threadIdx.x; d < D; d += blockDim.x) qs[d] = qp[d];
-    __syncthreads();
-    int lo = chunk > 0 ? (pos / chunk) * chunk : 0;
-    if (window > 0) lo = max(lo, pos - window + 1);
-    const int32_t* bt = st.block_table + (int64_t)e * st.max_blocks;
+// ---- attend -----------------------------------------------------------------------------------------------------------------------
+// One block of 256 threads per (tile of consecutive tokens of one entry, kv head, block of its query heads, split of the keys).
+// Its rows are (token, query head) pairs, RQ = 16 * RT of them (RT = 4: prompt portions; RT = 1: steps of few tokens); the keys the
+// rows can see are walked in tiles of 64: K and V rows come through the block table into shared memory with coalesced loads, the
+// scores of the tile are an f32 register-tiled product (thread (ty, tx): rows ty * RT + i, keys tx + 16 j), the soft-max is kept
+// online per row (maximum and sum in f32, reduced over the 16 lanes of a row), the weights go through shared memory into the second
+// product (value columns 4 tx + u + 64 j).  Key tiles are dealt round-robin to `nsplit` blocks when there are too few rows to fill
+// the GPU (decode); the partial (maximum, sum, weighted values) of each split is merged by attn_merge_kernel.
+constexpr int AT_KT = 64;
+constexpr int AT_NT = 256;
+
+struct AttnArgs {
+    const float* qkvg;
+    int64_t ld;
+    const float *kpool, *vpool;
+    int H, G, D, V, Rb, HB, QT, nsplit;
+    float scale;
+    int chunk, window, gated;
+    void* out;
+    int out_dtype;
+    float* part;   // [T][H][nsplit][V + 2] when nsplit > 1
+    int* err;
+};
+
+__device__ __forceinline__ bool attn_find_tile(const b200seq_step& st, int idx, int QT, int& e, int& t0, int& nq) {
+    int acc = 0;
+    for (e = 0; e < st.B; ++e) {
+        const int s0 = st.ent_start[e], n = st.ent_start[e + 1] - s0;
+        const int nt = (n + QT - 1) / QT;
+        if (idx < acc + nt) {
+            const int local = idx - acc;
+            t0 = s0 + local * QT;
+            nq = min(QT, n - local * QT);
+            return true;
+        }
+        acc += nt;
+    }
+    return false;
+}
+
+__device__ __forceinline__ float dot4(const float4 a, const float4 b, float acc) {
+    acc = fmaf(a.x, b.x, acc), acc = fmaf(a.y, b.y, acc), acc = fmaf(a.z, b.z, acc), acc = fmaf(a.w, b.w, acc);
+    return acc;
+}
+
+template <int RT, int VPT>
+__global__ void __launch_bounds__(AT_NT) attn_tile_kernel(const AttnArgs a, const b200seq_step st) {
+    extern __shared__ __align__(16) float sm[];
+    constexpr int RQ = 16 * RT, VS = 16 * VPT, PS = AT_KT + 4;
+    const int D = a.D, V = a.V, H = a.H, G = a.G;
+    const int Dp = (D + 3) & ~3, QS = Dp + 4;
+    float* Qs = sm;                     // [RQ][QS]
+    float* Ks = Qs + RQ * QS;           // [AT_KT][QS]
+    float* Vs = Ks + AT_KT * QS;        // [AT_KT][VS]
+    float* Ps = Vs + AT_KT * VS;        // [RQ][PS]
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    int e, t0, nq;
+    if (!attn_find_tile(st, blockIdx.x, a.QT, e, t0, nq)) return;
+    const int g = blockIdx.y / a.HB, hb = blockIdx.y - g * a.HB;
+    const int R = H / G;
+    const int h0 = g * R + hb * a.Rb, nh = min(a.Rb, R - hb * a.Rb);
+    const int split = blockIdx.z;
+    const int p0 = st.tok_pos[t0], hi = p0 + nq - 1;
     const int bs = st.block_size;
-    if (pos / bs >= st.max_blocks) {
-        if (threadIdx.x == 0) atomicOr(err, 1);
+    const int32_t* bt = st.block_table + (int64_t)e * st.max_blocks;
+    if (hi / bs >= st.max_blocks || p0 < 0) {
+        if (tid == 0) atomicOr(a.err, 1);
         return;
     }
-    float m = -INFINITY, l = 0.f, acc[ATT_VR];
+    int kbeg = a.chunk > 0 ? (p0 / a.chunk) * a.chunk : 0;
+    if (a.window > 0) kbeg = max(kbeg, p0 - a.window + 1);
+    // queries (zero rows where the tile has no token or the block no head)
+    for (int idx = tid; idx < RQ * Dp; idx += AT_NT) {
+        const int r = idx / Dp, d = idx - r * Dp;
+        const int tq = r / a.Rb, hr = r - tq * a.Rb;
+        Qs[r * QS + d] = (tq < nq && hr < nh && d < D) ? a.qkvg[(int64_t)(t0 + tq) * a.ld + (int64_t)(h0 + hr) * D + d] : 0.f;
+    }
+    // per-row limits of the visible keys
+    int rlo[RT], rhi[RT];
+    float m[RT], l[RT], acc[RT][VPT];
 #pragma unroll
-    for (int i = 0; i < ATT_VR; ++i) acc[i] = 0.f;
-    const bool d4 = (D & 3) == 0;
-    for (int base = lo + wid * 32; base <= pos; base += ATT_WARPS * 32) {
-        const int kp = base + lane;
-        float s = -INFINITY;
-        if (kp <= pos) {
-            const int64_t row = (int64_t)bt[kp / bs] * bs + kp % bs;
-            const float* kr = kpool + (row * G + g) * D;
-            float a = 0.f;
-            if (d4) {
-                for (int d = 0; d < D; d += 4) {
-                    const float4 kv = *reinterpret_cast<const float4*>(kr + d);
-                    a = fmaf(qs[d], kv.x, a), a = fmaf(qs[d + 1], kv.y, a), a = fmaf(qs[d + 2], kv.z, a), a = fmaf(qs[d + 3], kv.w, a);
+    for (int i = 0; i < RT; ++i) {
+        const int r = ty * RT + i;
+        const int tq = r / a.Rb, hr = r - tq * a.Rb;
+        if (tq < nq && hr < nh) {
+            const int p = p0 + tq;
+            int lo = a.chunk > 0 ? (p / a.chunk) * a.chunk : 0;
+            if (a.window > 0) lo = max(lo, p - a.window + 1);
+            rlo[i] = lo, rhi[i] = p;
+        } else {
+            rlo[i] = 1, rhi[i] = 0;   // sees nothing
+        }
+        m[i] = -INFINITY, l[i] = 0.f;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) acc[i][j] = 0.f;
+    }
+    const bool vecD = (D & 3) == 0, vecV = (V & 3) == 0;
+    int tile = 0;
+    for (int k0 = kbeg; k0 <= hi; k0 += AT_KT, ++tile) {
+        if (tile % a.nsplit != split) continue;
+        __syncthreads();   // the previous tile's products are done with Ks, Vs, Ps (and Qs is written before the first)
+        if (vecD) {
+            const int d4n = D >> 2;
+            for (int idx = tid; idx < AT_KT * d4n; idx += AT_NT) {
+                const int k = idx / d4n, d4 = idx - k * d4n;
+                const int kp = k0 + k;
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (kp <= hi) v = *reinterpret_cast<const float4*>(a.kpool + (((int64_t)bt[kp / bs] * bs + kp % bs) * G + g) * D + 4 * d4);
+                *reinterpret_cast<float4*>(Ks + k * QS + 4 * d4) = v;
+            }
+        } else {
+            for (int idx = tid; idx < AT_KT * Dp; idx += AT_NT) {
+                const int k = idx / Dp, d = idx - k * Dp;
+                const int kp = k0 + k;
+                Ks[k * QS + d] = (kp <= hi && d < D) ? a.kpool[(((int64_t)bt[kp / bs] * bs + kp % bs) * G + g) * D + d] : 0.f;
+            }
+        }
+        if (vecV) {
+            for (int idx = tid; idx < AT_KT * (VS >> 2); idx += AT_NT) {
+                const int k = idx / (VS >> 2), c4 = idx - k * (VS >> 2);
+                const int kp = k0 + k;
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (kp <= hi && 4 * c4 < V) v = *reinterpret_cast<const float4*>(a.vpool + (((int64_t)bt[kp / bs] * bs + kp % bs) * G + g) * V + 4 * c4);
+                *reinterpret_cast<float4*>(Vs + k * VS + 4 * c4) = v;
+            }
+        } else {
+            for (int idx = tid; idx < AT_KT * VS; idx += AT_NT) {
+                const int k = idx / VS, c = idx - k * VS;
+                const int kp = k0 + k;
+                Vs[k * VS + c] = (kp <= hi && c < V) ? a.vpool[(((int64_t)bt[kp / bs] * bs + kp % bs) * G + g) * V + c] : 0.f;
+            }
+        }
+        __syncthreads();
+        float s[RT][4];
+#pragma unroll
+        for (int i = 0; i < RT; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) s[i][j] = 0.f;
+        for (int d = 0; d < Dp; d += 4) {
+            float4 q[RT], k[4];
+#pragma unroll
+            for (int i = 0; i < RT; ++i) q[i] = *reinterpret_cast<const float4*>(Qs + (ty * RT + i) * QS + d);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) k[j] = *reinterpret_cast<const float4*>(Ks + (tx + 16 * j) * QS + d);
+#pragma unroll
+            for (int i = 0; i < RT; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) s[i][j] = dot4(q[i], k[j], s[i][j]);
+        }
+#pragma unroll
+        for (int i = 0; i < RT; ++i) {
+            float mx = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int kp = k0 + tx + 16 * j;
+                s[i][j] = (kp >= rlo[i] && kp <= rhi[i]) ? s[i][j] * a.scale : -INFINITY;
+                mx = fmaxf(mx, s[i][j]);
+            }
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+            const float mn = fmaxf(m[i], mx);
+            float corr = 1.f, sum = 0.f;
+            if (mn != -INFINITY) {
+                corr = expf(m[i] - mn);   // m = -inf before the first visible key: 0
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    s[i][j] = s[i][j] == -INFINITY ? 0.f : expf(s[i][j] - mn);
+                    sum += s[i][j];
                 }
             } else {
-                for (int d = 0; d < D; ++d) a = fmaf(qs[d], kr[d], a);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) s[i][j] = 0.f;
             }
-            s = a * scale;
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            l[i] = l[i] * corr + sum;
+            m[i] = mn;
+#pragma unroll
+            for (int j = 0; j < VPT; ++j) acc[i][j] *= corr;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) Ps[(ty * RT + i) * PS + tx + 16 * j] = s[i][j];
         }
-        const float mn = fmaxf(m, warp_max(s));
-        const float corr = expf(m - mn);   // m = -inf on the first tile: exp(-inf) = 0
-        const float p = kp <= pos ? expf(s - mn) : 0.f;
-        l = l * corr + warp_sum(p);
+        __syncthreads();
+        for (int k = 0; k < AT_KT; k += 4) {
+            float4 p[RT];
 #pragma unroll
-        for (int i = 0; i < ATT_VR; ++i) acc[i] *= corr;
-        m = mn;
-        const int nk = min(32, pos - base + 1);
-        for (int j = 0; j < nk; ++j) {
-            const float pj = __shfl_sync(0xffffffffu, p, j);
-            const int kj = base + j;
-            const int64_t row = (int64_t)bt[kj / bs] * bs + kj % bs;
-            const float* vr = vpool + (row * G + g) * V;
+            for (int i = 0; i < RT; ++i) p[i] = *reinterpret_cast<const float4*>(Ps + (ty * RT + i) * PS + k);
 #pragma unroll
-            for (int i = 0; i < ATT_VR; ++i) {
-                const int d = lane + 32 * i;
-                if (d < V) acc[i] = fmaf(pj, vr[d], acc[i]);
+            for (int kk = 0; kk < 4; ++kk) {
+#pragma unroll
+                for (int jv = 0; jv < VPT / 4; ++jv) {
+                    const float4 v = *reinterpret_cast<const float4*>(Vs + (k + kk) * VS + jv * 64 + tx * 4);
+#pragma unroll
+                    for (int i = 0; i < RT; ++i) {
+                        const float pv = kk == 0 ? p[i].x : kk == 1 ? p[i].y : kk == 2 ? p[i].z : p[i].w;
+                        acc[i][4 * jv] = fmaf(pv, v.x, acc[i][4 * jv]);
+                        acc[i][4 * jv + 1] = fmaf(pv, v.y, acc[i][4 * jv + 1]);
+                        acc[i][4 * jv + 2] = fmaf(pv, v.z, acc[i][4 * jv + 2]);
+                        acc[i][4 * jv + 3] = fmaf(pv, v.w, acc[i][4 * jv + 3]);
+                    }
+                }
             }
         }
     }
-    if (lane == 0) wm[wid] = m, wl[wid] = l;
 #pragma unroll
-    for (int i = 0; i < ATT_VR; ++i) {
-        const int d = lane + 32 * i;
-        if (d < V) wacc[wid * V + d] = acc[i];
+    for (int i = 0; i < RT; ++i) {
+        const int r = ty * RT + i;
+        const int tq = r / a.Rb, hr = r - tq * a.Rb;
+        if (tq >= nq || hr >= nh) continue;
+        const int t = t0 + tq, h = h0 + hr;
+        if (a.nsplit == 1) {
+            float gate = 1.f;
+            if (a.gated) gate = sigmoidf_acc(a.qkvg[(int64_t)t * a.ld + (int64_t)(H + G) * D + (int64_t)G * V + h]);
+            const float f = gate / l[i];
+#pragma unroll
+            for (int jv = 0; jv < VPT / 4; ++jv)
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int c = jv * 64 + tx * 4 + u;
+                    if (c < V) store_act(a.out, a.out_dtype, ((int64_t)t * H + h) * V + c, acc[i][4 * jv + u] * f);
+                }
+        } else {
+            float* pp = a.part + (((int64_t)t * H + h) * a.nsplit + split) * (V + 2);
+            if (tx == 0) pp[0] = m[i], pp[1] = l[i];
+#pragma unroll
+            for (int jv = 0; jv < VPT / 4; ++jv)
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int c = jv * 64 + tx * 4 + u;
+                    if (c < V) pp[2 + c] = acc[i][4 * jv + u];
+                }
+        }
     }
-    __syncthreads();
+}
+
+// grid (T, H): merges the splits of one (token, head) in split order
+__global__ void attn_merge_kernel(const AttnArgs a) {
+    const int t = blockIdx.x, h = blockIdx.y;
+    const int V = a.V, ns = a.nsplit;
+    const float* pp = a.part + ((int64_t)t * a.H + h) * ns * (V + 2);
     float M = -INFINITY;
-    for (int w = 0; w < ATT_WARPS; ++w) M = fmaxf(M, wm[w]);
+    for (int s = 0; s < ns; ++s) M = fmaxf(M, pp[s * (V + 2)]);
     float L = 0.f;
-    for (int w = 0; w < ATT_WARPS; ++w) L += wm[w] == -INFINITY ? 0.f : wl[w] * expf(wm[w] - M);
-    float gate = 1.f;
-    if (gated) gate = sigmoidf_acc(qkvg[(int64_t)t * ld + (int64_t)(H + G) * D + (int64_t)G * V + h]);
-    for (int d = threadIdx.x; d < V; d += blockDim.x) {
-        float o = 0.f;
-        for (int w = 0; w < ATT_WARPS; ++w)
-            if (wm[w] != -INFINITY) o = fmaf(wacc[w * V + d], expf(wm[w] - M), o);
-        store_act(out, out_dtype, (int64_t)t * H * V + (int64_t)h * V + d, o / L * gate);
+    for (int s = 0; s < ns; ++s) {
+        const float ms = pp[s * (V + 2)];
+        if (ms != -INFINITY) L = fmaf(pp[s * (V + 2) + 1], expf(ms - M), L);
     }
+    float gate = 1.f;
+    if (a.gated) gate = sigmoidf_acc(a.qkvg[(int64_t)t * a.ld + (int64_t)(a.H + a.G) * a.D + (int64_t)a.G * V + h]);
+    for (int c = threadIdx.x; c < V; c += blockDim.x) {
+        float o = 0.f;
+        for (int s = 0; s < ns; ++s) {
+            const float ms = pp[s * (V + 2)];
+            if (ms != -INFINITY) o = fmaf(pp[s * (V + 2) + 2 + c], expf(ms - M), o);
+        }
+        store_act(a.out, a.out_dtype, ((int64_t)t * a.H + h) * V + c, o / L * gate);
+    }
+}
+
+struct AttnPlan {
+    int RT, Rb, HB, QT, tiles, nsplit;
+};
+
+// how a step of T tokens in B entries is cut; max_keys bounds the keys one token can see
+static AttnPlan attn_plan(int T, int B, int H, int G, int max_keys) {
+    AttnPlan p;
+    const int R = H / G;
+    p.RT = T > 16 ? 4 : 1;
+    const int RQ = 16 * p.RT;
+    p.Rb = R < RQ ? R : RQ;
+    p.HB = (R + p.Rb - 1) / p.Rb;
+    p.QT = RQ / p.Rb;
+    p.tiles = (T + p.QT - 1) / p.QT + B;   // upper bound of the step's query tiles
+    const int real = (T + p.QT - 1) / p.QT * G * p.HB;
+    int ns = (2 * 148 + real - 1) / real;
+    const int kt = (max_keys + AT_KT - 1) / AT_KT;
+    ns = ns < kt ? ns : kt;
+    p.nsplit = ns < 1 ? 1 : (ns > 32 ? 32 : ns);
+    return p;
 }
 
 }  // namespace b200seq
@@ -151,17 +345,55 @@ int b200seq_attn_prep(float* qkvg, int64_t ld, const b200seq_step* st, float* kp
     return 0;
 }
 
+size_t b200seq_attn_scratch_floats(int T, int B, int H, int G, int V, int max_keys) {
+    if (T < 1 || B < 1 || H < 1 || G < 1 || H % G) return 0;
+    const AttnPlan p = attn_plan(T, B, H, G, max_keys);
+    return p.nsplit > 1 ? (size_t)T * H * p.nsplit * (V + 2) : 0;
+}
+
 int b200seq_attn(const float* qkvg, int64_t ld, const b200seq_step* st, const float* kpool, const float* vpool, int H, int G, int D, int V, float scale,
-                 int chunk, int window, int gated, void* out, int out_dtype, void* stream) {
-    if (!qkvg || !st || !kpool || !vpool || !out || H < 1 || G < 1 || H % G || D < 1 || V < 1 || V > 32 * ATT_VR)
-        return fail(B200SEQ_ERR_INVALID_ARG, "attn: bad arguments (value size <= %d)", 32 * ATT_VR);
+                 int chunk, int window, int gated, void* out, int out_dtype, float* scratch, size_t scratch_floats, void* stream) {
+    if (!qkvg || !st || !kpool || !vpool || !out || H < 1 || G < 1 || H % G || D < 1 || V < 1 || V > 256)
+        return fail(B200SEQ_ERR_INVALID_ARG, "attn: bad arguments (value size <= 256)");
     if (st->T == 0) return 0;
-    const size_t smem = ((size_t)D + 2 * ATT_WARPS + (size_t)ATT_WARPS * V) * sizeof(float);
-    if (smem > 48 * 1024) return fail(B200SEQ_ERR_UNSUPPORTED, "attn: head size too large");
-    dim3 grid(st->T, H);
-    attn_kernel<<<grid, ATT_WARPS * 32, smem, (cudaStream_t)stream>>>(qkvg, ld, *st, kpool, vpool, H, G, D, V, scale, chunk, window, gated, out, out_dtype,
-                                                                      error_flag_dev());
+    int max_keys = st->max_blocks * st->block_size;
+    if (chunk > 0 && chunk < max_keys) max_keys = chunk;
+    if (window > 0 && window < max_keys) max_keys = window;
+    AttnPlan p = attn_plan(st->T, st->B, H, G, max_keys);
+    if (p.nsplit > 1 && (!scratch || scratch_floats < (size_t)st->T * H * p.nsplit * (V + 2))) p.nsplit = 1;
+    AttnArgs a{qkvg, ld, kpool, vpool, H, G, D, V, p.Rb, p.HB, p.QT, p.nsplit, scale, chunk, window, gated, out, out_dtype, scratch, error_flag_dev()};
+    const int VPT = V <= 64 ? 4 : (V <= 128 ? 8 : 16);
+    const int RQ = 16 * p.RT, QS = ((D + 3) & ~3) + 4;
+    const size_t smem = ((size_t)(RQ + AT_KT) * QS + (size_t)AT_KT * 16 * VPT + (size_t)RQ * (AT_KT + 4)) * sizeof(float);
+    if (smem > 220 * 1024) return fail(B200SEQ_ERR_UNSUPPORTED, "attn: head size too large");
+    dim3 grid(p.tiles, G * p.HB, p.nsplit);
+    cudaStream_t cs = (cudaStream_t)stream;
+    cudaError_t e = cudaSuccess;
+#define ATT_LAUNCH(RT_, VPT_)                                                                                                   \
+    do {                                                                                                                        \
+        static size_t set_ = 0;                                                                                                 \
+        if (smem > 48 * 1024 && smem > set_) {                                                                                  \
+            e = cudaFuncSetAttribute(attn_tile_kernel<RT_, VPT_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
+            set_ = smem;                                                                                                        \
+        }                                                                                                                       \
+        if (e == cudaSuccess) attn_tile_kernel<RT_, VPT_><<<grid, AT_NT, smem, cs>>>(a, *st);                                   \
+    } while (0)
+    if (p.RT == 4) {
+        if (VPT == 4) ATT_LAUNCH(4, 4);
+        else if (VPT == 8) ATT_LAUNCH(4, 8);
+        else ATT_LAUNCH(4, 16);
+    } else {
+        if (VPT == 4) ATT_LAUNCH(1, 4);
+        else if (VPT == 8) ATT_LAUNCH(1, 8);
+        else ATT_LAUNCH(1, 16);
+    }
+#undef ATT_LAUNCH
+    if (e != cudaSuccess) return cuda_status(e, "attn attribute");
     SEQ_LAUNCH_CHECK("attn");
+    if (p.nsplit > 1) {
+        attn_merge_kernel<<<dim3(st->T, H), V <= 64 ? 64 : 128, 0, cs>>>(a);
+        SEQ_LAUNCH_CHECK("attn merge");
+    }
     return 0;
 }
 

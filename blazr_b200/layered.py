@@ -96,6 +96,7 @@ class _Workspace:
         self.inner_a = torch.empty((cap, max(1, model.max_inner)), **act)
         self.fin = torch.empty((cap, W), **act)
         self.logits = torch.empty((cap, cfg.vocab), **f32)
+        self.scratch = torch.empty(max(1, model.scratch_floats(cap)), **f32)      # work area: segmented state-space scan, key-split attention
         self.next_ids = torch.empty((cap,), dtype=torch.int32, device=dev)
         # int32 step arrays in one buffer: ids | ent | pos | want | start | slot | pos0 | block_table
         B, mb = model.max_seqs, model.max_blocks
@@ -214,6 +215,24 @@ class LayeredModel:
         self._ws.clear()
         self._graphs.clear()
 
+    def scratch_floats(self, cap: int) -> int:
+        """floats of the largest work area any layer wants for a step of up to `cap` tokens"""
+        need = 0
+        seen = set()
+        for L in self.layers:
+            m = L["spec"].mixer
+            if L["spec"].kind == "ssm":
+                need = max(need, seqops.ssm_scratch_floats(cap, self.max_seqs, m.heads, m.vdim, m.state))
+            else:
+                keys = self.max_blocks * self.block_size
+                keys = min(keys, m.chunk) if m.chunk > 0 else keys
+                keys = min(keys, m.window) if m.window > 0 else keys
+                key = (m.heads, m.kv_heads, m.vdim, keys)
+                if key not in seen:     # the split count falls as the step grows: the largest need is at some T <= cap
+                    seen.add(key)
+                    need = max([need] + [seqops.attn_scratch_floats(T, 1, m.heads, m.kv_heads, m.vdim, keys) for T in range(1, cap + 1)])
+        return need
+
     def cache_bytes(self) -> int:
         keys = ("canon1_state", "canon2_state", "kpool", "vpool", "conv_state", "ssm_state")
         return sum(L[k].numel() * 4 for L in self.layers for k in keys if k in L)
@@ -321,7 +340,7 @@ class LayeredModel:
         seqops.linear(a, L["w_in"], qkvg)
         seqops.attn_prep(qkvg, st, L["kpool"], L["vpool"], m.heads, m.kv_heads, m.dim, m.vdim, self.cfg.eps if m.qk_unit_norm else -1.0)
         o = ws.inner_a.view(-1)[:T * m.heads * m.vdim].view(T, m.heads * m.vdim)
-        seqops.attn(qkvg, st, L["kpool"], L["vpool"], m.heads, m.kv_heads, m.dim, m.vdim, m.scale, m.chunk, m.window, m.gated, o)
+        seqops.attn(qkvg, st, L["kpool"], L["vpool"], m.heads, m.kv_heads, m.dim, m.vdim, m.scale, m.chunk, m.window, m.gated, o, ws.scratch)
         seqops.linear(o, L["w_o"], y)
 
     def _ssm(self, L, m: SsmSpec, ws: _Workspace, st, T: int, a: torch.Tensor, y: torch.Tensor) -> None:
@@ -332,7 +351,7 @@ class LayeredModel:
         xbc = ws.xbc.view(-1)[:T * (inner + 2 * gn)].view(T, inner + 2 * gn)
         seqops.causal_conv(proj[:, inner:2 * inner + 2 * gn], L["conv_w"], L["conv_b"], L["conv_state"], st, seqops.CONV_SILU, xbc)
         yg = ws.inner_f.view(-1)[:T * inner].view(T, inner)
-        seqops.ssm_scan(proj, 0, 2 * inner + 2 * gn, xbc, L["A_log"], L["D"], L["dt_bias"], L["ssm_state"], st, m.heads, m.vdim, m.state, m.groups, yg)
+        seqops.ssm_scan(proj, 0, 2 * inner + 2 * gn, xbc, L["A_log"], L["D"], L["dt_bias"], L["ssm_state"], st, m.heads, m.vdim, m.state, m.groups, yg, ws.scratch)
         yn = ws.inner_a.view(-1)[:T * inner].view(T, inner)
         seqops.group_rmsnorm(yg, L["mnorm"], m.norm_groups, self.cfg.eps, yn)
         seqops.linear(yn, L["w_o"], y)

@@ -1,0 +1,374 @@
+"""Throughput of a layer-list design at sizes that resemble a real model's layers (random weights), beside the framework's
+dense-attention decoder (blazr_b200/decode.py, Q8_0 weights) of the same width, head layout, feed-forward size and layer count:
+
+    prefill  : one prompt of S tokens as one engine step (tokens/s)
+    decode   : B live requests with `ctx` tokens each, one token per request per step (tokens/s; CUDA-graph replay)
+    kernels  : every operator of one prefill step and one decode step timed alone (CUDA events around each launch), with its
+               algorithmic bytes / FLOPs and the fraction of the roofline it reaches; the like kernels of the decoder beside them
+
+`python bench.py --layered fenorax [--layered-sizes w1024,w2048]` prints the result as one JSON line; bench.py's default workload
+and contract are untouched.
+"""
+from __future__ import annotations
+
+import json
+import os
+from typing import Dict, List
+
+import numpy as np
+import torch
+
+from . import seqops
+from .engine import Engine
+from .layered import LayeredModel
+
+# sizes of one layer group; the layer list is [ssm, attention + ff, ssm, attention + ff]
+SIZES: Dict[str, dict] = {
+    "w1024": dict(width=1024, heads=16, kv_heads=4, dim=64, ff=4096, ssm_heads=32, ssm_vdim=64, state=64, ssm_groups=2, chunk=1024, vocab=32000),
+    "w2048": dict(width=2048, heads=32, kv_heads=8, dim=64, ff=8192, ssm_heads=64, ssm_vdim=64, state=128, ssm_groups=8, chunk=2048, vocab=32000),
+    "w4096": dict(width=4096, heads=32, kv_heads=8, dim=128, ff=14336, ssm_heads=128, ssm_vdim=64, state=128, ssm_groups=8, chunk=2048, vocab=32000),
+}
+F32_FMA_TFLOPS_NOMINAL = 148 * 128 * 2 * 1.965e9 / 1e12    # CUDA-core f32 rate at the maximum SM clock (not measured)
+
+
+def fenorax_config(sz: dict, streams: int = 2, taps: int = 3) -> dict:
+    ssm = {"type": "mamba2", "mlp": None,
+           "mixer": {"conv": 4, "groups": sz["ssm_groups"], "heads": sz["ssm_heads"], "norm_groups": sz["ssm_groups"], "state": sz["state"], "vdim": sz["ssm_vdim"]}}
+    att = {"type": "attention", "mlp": {"kind": "dense", "ff": sz["ff"], "limit": 7.0},
+           "mixer": {"dim": sz["dim"], "vdim": sz["dim"], "heads": sz["heads"], "kv_heads": sz["kv_heads"], "scale": sz["dim"] ** -0.5, "mask": {"size": sz["chunk"]}}}
+    return {"architecture": "Fenorax", "vocab": sz["vocab"], "width": sz["width"], "streams": streams, "norm": {"eps": 1e-5, "groups": 2}, "canon": {"taps": taps},
+            "embedding": {"scale": float(sz["width"]) ** 0.5}, "layers": [ssm, att, ssm, att]}
+
+
+def random_tensors(cfg: dict, device, seed: int = 7):
+    """name -> tensor function with random weights of the design's shapes, generated on the device"""
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    W, S, taps = cfg["width"], cfg["streams"], cfg["canon"]["taps"]
+
+    def rnd(*shape, scale=1.0, dtype=torch.bfloat16):
+        return (torch.randn(shape, generator=g, device=device) * scale).to(dtype)
+
+    t = {"embed": rnd(cfg["vocab"], W, scale=W ** -0.5), "final.norm": torch.ones(W, dtype=torch.bfloat16, device=device)}
+    for i, lay in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", lay["mixer"]
+        for q in ((1, 2) if lay["mlp"] else (1,)):
+            t[f"{p}norm{q}"] = torch.ones(W, dtype=torch.bfloat16, device=device)
+            t[f"{p}canon{q}"] = rnd(W, taps, scale=0.1)
+            t[f"{p}hc{q}.in"] = torch.full((S,), 1.0 / S, dtype=torch.bfloat16, device=device)
+            t[f"{p}hc{q}.out"] = torch.full((S,), 0.5, dtype=torch.bfloat16, device=device)
+            t[f"{p}hc{q}.mix"] = torch.eye(S, dtype=torch.bfloat16, device=device)
+        if lay["type"] == "mamba2":
+            inner, gn = m["heads"] * m["vdim"], m["groups"] * m["state"]
+            t[p + "mix.in"] = rnd(2 * inner + 2 * gn + m["heads"], W, scale=W ** -0.5)
+            t[p + "mix.o"] = rnd(W, inner, scale=inner ** -0.5)
+            t[p + "mix.conv"] = rnd(inner + 2 * gn, m["conv"], scale=0.3)
+            t[p + "mix.conv.b"] = rnd(inner + 2 * gn, scale=0.1)
+            t[p + "mix.dt_bias"] = rnd(m["heads"], scale=0.5)
+            t[p + "mix.A_log"] = rnd(m["heads"], scale=0.5)
+            t[p + "mix.D"] = rnd(m["heads"])
+            t[p + "mix.norm"] = torch.ones(inner, dtype=torch.bfloat16, device=device)
+        else:
+            H, G, D, V = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            t[p + "mix.q"], t[p + "mix.k"], t[p + "mix.v"] = rnd(H * D, W, scale=W ** -0.5), rnd(G * D, W, scale=W ** -0.5), rnd(G * V, W, scale=W ** -0.5)
+            t[p + "mix.g"], t[p + "mix.o"] = rnd(H, W, scale=W ** -0.5), rnd(W, H * V, scale=(H * V) ** -0.5)
+        if lay["mlp"]:
+            ff = lay["mlp"]["ff"]
+            t[p + "mlp.gate"], t[p + "mlp.up"], t[p + "mlp.down"] = rnd(ff, W, scale=W ** -0.5), rnd(ff, W, scale=W ** -0.5), rnd(W, ff, scale=ff ** -0.5)
+    return t.__getitem__
+
+
+def _events():
+    return torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+
+def _linear_weights(model: LayeredModel) -> int:
+    return sum(L[k].numel() for L in model.layers for k in ("w_in", "w_o", "w_gu", "w_down") if k in L)
+
+
+# ---- cost model: algorithmic bytes and FLOPs of one operator call, from the shapes the timeline recorded ---------------------------
+def _cost(name: str, shapes, scal, scen: dict):
+    sh = [s for s in shapes if s is not None]
+    by = lambda s: int(np.prod(s[0])) * s[1]
+    if name in ("linear", "linear_gated"):
+        (xs, xe), (ws, _), (ys, ye) = sh[0], sh[1], sh[2]
+        M, K, N = xs[0], xs[1], ws[0]
+        return M * K * xe + N * K * 2 + int(np.prod(ys)) * ye, 2.0 * M * N * K, "tensor"
+    if name == "attn":
+        T, H, G, D, V = sh[0][0][0], scal[0], scal[1], scal[2], scal[3]
+        keys = scen["visible_keys"]                              # sum over the step's tokens of the keys each one sees
+        kv_once = scen["kv_rows_touched"] * G * (D + V) * 4      # every visible K / V row once
+        return kv_once + T * H * (D + V) * 4, 2.0 * keys * H * (D + V), "f32" if scen["prefill"] else "hbm"
+    if name == "ssm_scan":
+        T, (H, V, N, G) = sh[0][0][0], scal[2:6]
+        B = scen["entries"]
+        return T * (2 * H * V + 2 * G * N + H) * 4 + T * H * V * 4 + 2 * B * H * N * V * 4, 4.0 * T * H * V * N, "f32" if scen["prefill"] else "hbm"
+    # elementwise / normalising operators: every tensor argument once (in-place stream update: read + write)
+    total = sum(by(s) for s in sh)
+    if name == "hc_norm" and len(sh) >= 2 and shapes[1] is not None:
+        total += by(sh[0])
+    return total, 0.0, "hbm"
+
+
+def _roof_us(bytes_, flops, kind, pk) -> float:
+    t_mem = bytes_ / (pk["hbm_gbs"] * 1e9)
+    t_fl = flops / ((pk["bf16_tflops"] if kind == "tensor" else F32_FMA_TFLOPS_NOMINAL) * 1e12) if kind in ("tensor", "f32") else 0.0
+    return max(t_mem, t_fl) * 1e6
+
+
+def kernel_table(model: LayeredModel, eng: Engine, run, scen: dict, pk) -> List[dict]:
+    """runs `run()` (one engine step) with the operator timeline on and sums time and cost per operator (linear layers per shape)"""
+    graphs = model.use_graphs
+    model.use_graphs = False
+    try:
+        seqops.timeline = []
+        run()
+        torch.cuda.synchronize()
+        tl, seqops.timeline = seqops.timeline, None
+    finally:
+        seqops.timeline = None
+        model.use_graphs = graphs
+    agg: Dict[str, dict] = {}
+    for name, shapes, scal, e0, e1 in tl:
+        key = name
+        if name in ("linear", "linear_gated"):
+            sh = [s for s in shapes if s is not None]
+            key = f"{name} M={sh[0][0][0]} N={sh[1][0][0]} K={sh[0][0][1]}"
+        b, f, kind = _cost(name, shapes, scal, scen)
+        a = agg.setdefault(key, dict(op=key, calls=0, us=0.0, bytes=0, flops=0.0, roof_us=0.0, bound=kind))
+        a["calls"] += 1
+        a["us"] += e0.elapsed_time(e1) * 1e3
+        a["bytes"] += b
+        a["flops"] += f
+        a["roof_us"] += _roof_us(b, f, kind, pk)
+    rows = []
+    for a in agg.values():
+        a["frac_of_roofline"] = round(a["roof_us"] / a["us"], 4) if a["us"] > 0 else None
+        a["us"], a["roof_us"] = round(a["us"], 1), round(a["roof_us"], 1)
+        rows.append(a)
+    rows.sort(key=lambda r: -r["us"])
+    return rows
+
+
+# ---- the design's arm ----------------------------------------------------------------------------------------------------------------
+def bench_layered(design: str, size: str, pk, S: int = 4096, ctx: int = 1024, batches=(1, 4), steps: int = 32, dtype: str = "bfloat16") -> dict:
+    from . import registry
+    if design.lower() != "fenorax":
+        raise ValueError(f"no synthetic workload for design '{design}'")
+    sz = SIZES[size]
+    cfg = fenorax_config(sz)
+    dev = torch.device("cuda", torch.cuda.current_device())
+    model = LayeredModel(registry.LAYERED["Fenorax"](cfg), random_tensors(cfg, dev), dev, dtype)
+    Bmax = max(batches)
+    eng = Engine(model, max_tokens=max(S, Bmax * (ctx + steps + 64)) + 64, max_seqs=Bmax, max_step_tokens=max(S, 2048), prefill_chunk=S)
+    rng = np.random.default_rng(3)
+    prompt = rng.integers(0, sz["vocab"], S).tolist()
+    out = {"size": size, "config": {k: sz[k] for k in sz}, "layers": [l["type"] + ("+ff" if l["mlp"] else "") for l in cfg["layers"]], "streams": cfg["streams"],
+           "linear_weights": _linear_weights(model), "weight_bytes": model.weight_bytes}
+    lin_flops_tok = 2.0 * (_linear_weights(model) + 0)
+
+    # prefill: whole prompt in one step, logits of the last token, device timed; then through run_entries (host arrays in, logits out)
+    def prefill_once():
+        eng._forward([("p", prompt, [S - 1])])
+        eng.release("p")
+
+    for _ in range(3):
+        prefill_once()
+    torch.cuda.synchronize()
+    e0, e1 = _events()
+    reps = 5
+    e0.record()
+    for _ in range(reps):
+        prefill_once()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / reps
+    e0, e1 = _events()
+    e0.record()
+    for _ in range(reps):
+        eng.run_entries([{"id": "p", "tokens": prompt, "want": [S - 1]}], end=["p"])
+    e1.record()
+    torch.cuda.synchronize()
+    ms_e2e = e0.elapsed_time(e1) / reps
+    out["prefill"] = {"prompt_tokens": S, "ms": round(ms, 3), "tokens_per_s": round(S / ms * 1e3, 1), "e2e_tokens_per_s": round(S / ms_e2e * 1e3, 1),
+                      "linear_TFLOPs": round(lin_flops_tok * S / (ms * 1e-3) / 1e12, 1)}
+    chunk = sz["chunk"]
+    pos = np.arange(S)
+    scen = dict(prefill=True, entries=1, visible_keys=int((pos - (pos // chunk) * chunk + 1).sum()), kv_rows_touched=S)
+    out["prefill"]["kernels"] = kernel_table(model, eng, prefill_once, scen, pk)
+
+    # decode: B requests of ctx tokens, then one token each per step
+    out["decode"] = []
+    for B in batches:
+        ids = [f"d{b}" for b in range(B)]
+        for r in ids:
+            eng._forward([(r, rng.integers(0, sz["vocab"], ctx).tolist(), [])])
+        nxt = [[1]] * B
+
+        def dec_step():
+            eng._forward([(r, t, [0]) for r, t in zip(ids, nxt)], sample=True)
+
+        for _ in range(4):
+            dec_step()
+        torch.cuda.synchronize()
+        e0, e1 = _events()
+        e0.record()
+        for _ in range(steps):
+            dec_step()
+        e1.record()
+        torch.cuda.synchronize()
+        msd = e0.elapsed_time(e1) / steps
+        # end to end: token ids come back to the host every step and go in again (pinned upload inside the step)
+        e0, e1 = _events()
+        e0.record()
+        for _ in range(steps):
+            dec_step()
+            nxt = [[int(t)] for t in model.last_ids.cpu().tolist()]
+        e1.record()
+        torch.cuda.synchronize()
+        msd_e2e = e0.elapsed_time(e1) / steps
+        row = {"batch": B, "context": ctx, "ms_per_step": round(msd, 4), "tokens_per_s": round(B / msd * 1e3, 1), "e2e_tokens_per_s": round(B / msd_e2e * 1e3, 1),
+               "weight_GBs": round(model.weight_bytes / (msd * 1e-3) / 1e9, 1), "frac_hbm_weights_only": round(model.weight_bytes / (msd * 1e-3) / 1e9 / pk["hbm_gbs"], 3)}
+        held = eng.cache.live[ids[0]].n_tokens
+        lo = (held // chunk) * chunk
+        scen = dict(prefill=False, entries=B, visible_keys=B * (held - lo + 1), kv_rows_touched=B * (held - lo + 1))
+        row["kernels"] = kernel_table(model, eng, dec_step, scen, pk)
+        out["decode"].append(row)
+        for r in ids:
+            eng.release(r)
+    flags = seqops.error_flags()
+    if flags:
+        raise RuntimeError(f"device error flags {flags:#x}")
+    out["launches"] = seqops.launch_count()
+    del eng, model
+    torch.cuda.empty_cache()
+    return out
+
+
+# ---- the dense-attention decoder of equal size ---------------------------------------------------------------------------------------
+def bench_decoder(size: str, pk, S: int = 4096, ctx: int = 1024, batches=(1, 4), steps: int = 32, scheme: str = "Q8_0") -> dict:
+    """Same width, heads, feed-forward size, vocabulary and layer count; every layer is attention + feed-forward; weights Q8_0."""
+    import ctypes as C
+
+    from . import decode, ops
+    sz = SIZES[size]
+    cfg = decode.ModelConfig(f"dense-{size}", sz["width"], 4, sz["heads"], sz["kv_heads"], sz["dim"], sz["ff"], sz["vocab"], 10000.0)
+    client = ops.B200Client(torch.cuda.current_device())
+    rng = np.random.default_rng(3)
+    out = {"size": size, "scheme": scheme, "layers": 4}
+    d = decode.Decoder(client, cfg, scheme, batch=1, max_ctx=S + 16)
+    lin_w = sum(ln.w.N * ln.w.K for lay in d.layers for key in ("qkv", "o", "gu", "down") for ln in lay[key])
+    out["linear_weights"], out["weight_bytes"] = lin_w, d.weight_bytes
+    prompt = rng.integers(0, cfg.vocab, S)
+    for _ in range(2):
+        d.prefill(prompt)
+    torch.cuda.synchronize()
+    e0, e1 = _events()
+    reps = 3
+    e0.record()
+    for _ in range(reps):
+        d.prefill(prompt)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / reps
+    out["prefill"] = {"prompt_tokens": S, "ms": round(ms, 3), "tokens_per_s": round(S / ms * 1e3, 1), "linear_TFLOPs": round(2.0 * lin_w * S / (ms * 1e-3) / 1e12, 1),
+                      "note": "projections on the tcgen05 dequant-GEMM, attention of the prompt in torch SDPA (f16)"}
+    # like kernels, timed alone: the gate|up GEMM at M = S, the gate|up matvec at M = 1, the norm at M = S
+    kern = []
+    lay = d.layers[0]
+    gu = lay["gu"][0]
+    x = torch.randn((S, cfg.hidden), device=client.device)
+    y = torch.empty((S, gu.w.N), device=client.device)
+    ws = gu.w.workspace(S)
+    for _ in range(2):
+        client.quant_matmul(x, gu.w, out=y, workspace=ws)
+    e0, e1 = _events()
+    e0.record()
+    for _ in range(5):
+        client.quant_matmul(x, gu.w, out=y, workspace=ws)
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / 5
+    fl = 2.0 * S * gu.w.N * gu.w.K
+    roof = max(fl / (pk["bf16_tflops"] * 1e12), (gu.w.canonical_bytes + S * gu.w.K * 4 + S * gu.w.N * 4) / (pk["hbm_gbs"] * 1e9)) * 1e6
+    kern.append({"op": f"dequant GEMM gate|up M={S} N={gu.w.N} K={gu.w.K} (staging + tcgen05)", "us": round(us, 1), "roof_us": round(roof, 1), "frac_of_roofline": round(roof / us, 4),
+                 "bound": "tensor"})
+    del d, x, y, ws
+    torch.cuda.empty_cache()
+    out["decode"] = []
+    for B in batches:
+        d = decode.Decoder(client, cfg, scheme, batch=B, max_ctx=ctx + 3 * steps + 64)
+        d.capture()
+        d.reset([1] * B)
+        for b in range(B):
+            d.prefill(rng.integers(0, cfg.vocab, ctx), seq=b)
+        for _ in range(4):
+            d.replay()
+        torch.cuda.synchronize()
+        e0, e1 = _events()
+        e0.record()
+        for _ in range(steps):
+            d.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        msd = e0.elapsed_time(e1) / steps
+        row = {"batch": B, "context": ctx, "ms_per_step": round(msd, 4), "tokens_per_s": round(B / msd * 1e3, 1), "weight_GBs": round(d.weight_bytes / (msd * 1e-3) / 1e9, 1),
+               "frac_hbm_weights_only": round(d.weight_bytes / (msd * 1e-3) / 1e9 / pk["hbm_gbs"], 3), "launches_per_step": d.launches_per_step()}
+        if B == 1:
+            # attention of one decoded token over the context, every layer, timed alone (K / V rows of the context once per kv head)
+            st = ops._stream_ptr(client.device)
+            for lay in d.layers:
+                d._attention(lay, st)
+            torch.cuda.synchronize()
+            e0, e1 = _events()
+            e0.record()
+            for _ in range(5):
+                for lay in d.layers:
+                    d._attention(lay, st)
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) * 1e3 / (5 * len(d.layers))
+            held = int(d._host_pos)
+            by = held * cfg.n_kv_heads * cfg.head_dim * 2 * 4
+            kern.append({"op": f"attention decode, {held} keys, H={cfg.n_heads} G={cfg.n_kv_heads} D={cfg.head_dim}", "us": round(us, 2), "roof_us": round(by / (pk['hbm_gbs'] * 1e9) * 1e6, 2),
+                         "frac_of_roofline": round(by / (pk["hbm_gbs"] * 1e9) * 1e6 / us, 4), "bound": "hbm"})
+            gu = d.layers[0]["gu"][0]
+            xq = client.quantize_act(torch.randn((1, gu.w.K), device=client.device))
+            yv = torch.empty((1, gu.w.N), device=client.device)
+            wsv = gu.w.workspace(1)
+            gus = [lay["gu"][0] for lay in d.layers]
+            for g_ in gus:
+                client.matmul_q8(xq, 1, g_.w, out=yv, workspace=wsv)
+            e0, e1 = _events()
+            e0.record()
+            for _ in range(5):
+                for g_ in gus:
+                    client.matmul_q8(xq, 1, g_.w, out=yv, workspace=wsv)
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) * 1e3 / (5 * len(gus))
+            by = gu.w.canonical_bytes
+            kern.append({"op": f"matvec gate|up M=1 N={gu.w.N} K={gu.w.K} ({scheme})", "us": round(us, 2), "roof_us": round(by / (pk['hbm_gbs'] * 1e9) * 1e6, 2),
+                         "frac_of_roofline": round(by / (pk["hbm_gbs"] * 1e9) * 1e6 / us, 4), "bound": "hbm"})
+        out["decode"].append(row)
+        d.graph = None
+        del d
+        torch.cuda.empty_cache()
+    out["kernels"] = kern
+    return out
+
+
+def run(design: str, sizes: List[str], pk, pk_kind: str, S: int = 4096, ctx: int = 1024, steps: int = 32, clocks=None) -> dict:
+    res = {"metric": "layered_prefill_decode_tokens_per_s", "design": design, "dtype": "bf16 activations x bf16 weights, f32 accumulate; residual, norms, scores, state f32",
+           "data": "synthetic (random weights)", "peaks": {"hbm_gbs": pk["hbm_gbs"], "bf16_tflops": pk["bf16_tflops"], "kind": pk_kind, "f32_fma_tflops_nominal": round(F32_FMA_TFLOPS_NOMINAL, 1)},
+           "timing": "CUDA events, >= 3 warm-up runs; every prefill step streams activations larger than L2, decode weights are re-read from L2 / HBM as in serving",
+           "sizes": []}
+    for size in sizes:
+        row = {"size": size}
+        row[design.lower()] = bench_layered(design, size, pk, S=S, ctx=ctx, steps=steps)
+        try:
+            row["dense_decoder"] = bench_decoder(size, pk, S=S, ctx=ctx, steps=steps)
+        except Exception as ex:    # the comparison arm must not take the design's numbers down
+            row["dense_decoder"] = {"error": repr(ex)[:300]}
+        res["sizes"].append(row)
+    return res

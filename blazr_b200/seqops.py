@@ -28,8 +28,8 @@ TC_MIN_ROWS = 32   # b200seq_linear's automatic choice takes the tensor-core pat
 _DT = {torch.float32: F32, torch.bfloat16: BF16}
 
 EXPORTS = ["b200seq_last_error", "b200seq_version", "b200seq_launch_count", "b200seq_error_flags", "b200seq_embed_streams", "b200seq_hc_norm",
-           "b200seq_causal_conv", "b200seq_group_rmsnorm", "b200seq_gated_act", "b200seq_linear", "b200seq_linear_gated", "b200seq_attn_prep", "b200seq_attn",
-           "b200seq_ssm_scan", "b200seq_argmax"]
+           "b200seq_causal_conv", "b200seq_group_rmsnorm", "b200seq_gated_act", "b200seq_linear", "b200seq_linear_gated", "b200seq_attn_prep", "b200seq_attn", "b200seq_attn_scratch_floats",
+           "b200seq_ssm_scan", "b200seq_ssm_scratch_floats", "b200seq_argmax"]
 
 
 class SeqError(RuntimeError):
@@ -114,12 +114,39 @@ def _rows2d(t: torch.Tensor):
     return t.shape[0], t.shape[1], t.stride(0)
 
 
+# ---- per-operator timeline (bench / profiling aid): set `timeline = []` and every operator call appends
+#      (name, shapes of its tensor arguments, scalar arguments, start event, end event); None (default) costs nothing ----------
+timeline = None
+
+
+def _timed(fn):
+    name = fn.__name__
+
+    def wrap(*a, **k):
+        tl = timeline
+        if tl is None:
+            return fn(*a, **k)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        r = fn(*a, **k)
+        e1.record()
+        shapes = tuple((tuple(t.shape), t.element_size()) if isinstance(t, torch.Tensor) else None for t in a)
+        scal = tuple(t for t in a if isinstance(t, (int, float, bool)))
+        tl.append((name, shapes, scal, e0, e1))
+        return r
+
+    wrap.__name__, wrap.__doc__ = name, fn.__doc__
+    return wrap
+
+
 # ---- operators (all arguments are device tensors; outputs are written in place) --------------------------------------------
+@_timed
 def embed_streams(table: torch.Tensor, ids: torch.Tensor, scale: float, X: torch.Tensor):
     T, S, W = X.shape
     _check(lib().b200seq_embed_streams(_p(table), _p(ids), C.c_float(scale), T, S, W, _p(X), _st(X)))
 
 
+@_timed
 def hc_norm(X: torch.Tensor, y: Optional[torch.Tensor], post: Optional[torch.Tensor], in_w: Optional[torch.Tensor], norm_w: Optional[torch.Tensor],
             groups: int, eps: float, out: Optional[torch.Tensor], rows: Optional[torch.Tensor] = None):
     T, S, W = X.shape
@@ -127,6 +154,7 @@ def hc_norm(X: torch.Tensor, y: Optional[torch.Tensor], post: Optional[torch.Ten
     _check(lib().b200seq_hc_norm(_p(X), _p(y), _p(post), _p(in_w), _p(norm_w), S, W, groups, C.c_float(eps), _p(rows), R, _p(out), _DT[out.dtype] if out is not None else F32, _st(X)))
 
 
+@_timed
 def causal_conv(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], state: Optional[torch.Tensor], step: "StepDesc", mode: int, out: torch.Tensor):
     T, Cn, ldx = _rows2d(x)
     _, _, ldo = _rows2d(out)
@@ -134,18 +162,21 @@ def causal_conv(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], 
                                      C.c_int64(ldo), _st(x)))
 
 
+@_timed
 def group_rmsnorm(x: torch.Tensor, w: Optional[torch.Tensor], groups: int, eps: float, out: torch.Tensor):
     T, D, ldx = _rows2d(x)
     assert out.is_contiguous()
     _check(lib().b200seq_group_rmsnorm(_p(x), C.c_int64(ldx), _p(w), T, D, groups, C.c_float(eps), _p(out), _DT[out.dtype], _st(x)))
 
 
+@_timed
 def gated_act(gu: torch.Tensor, limit: float, alpha: float, up_shift: float, out: torch.Tensor, interleaved: bool = False):
     T, F2, ldg = _rows2d(gu)
     assert out.is_contiguous() and out.shape[1] * 2 == F2
     _check(lib().b200seq_gated_act(_p(gu), C.c_int64(ldg), T, F2 // 2, C.c_float(limit), C.c_float(alpha), C.c_float(up_shift), int(interleaved), _p(out), _DT[out.dtype], _st(gu)))
 
 
+@_timed
 def linear(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, path: int = PATH_AUTO):
     """y[M, N] (f32) = x[M, K] . w[N, K]^T; w bf16 contiguous"""
     M, K, ldx = _rows2d(x)
@@ -154,6 +185,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, path: int = PATH_A
     _check(lib().b200seq_linear(_p(x), _DT[x.dtype], C.c_int64(ldx), _p(w), M, N, K, _p(y), C.c_int64(ldy), path, _st(x)))
 
 
+@_timed
 def linear_gated(x: torch.Tensor, w_il: torch.Tensor, limit: float, alpha: float, up_shift: float, out: torch.Tensor):
     """out[M, F] = gated_act(x . w_il^T); w_il bf16 [2F, K] with alternating gate / up rows (tensor-core path only)"""
     M, K, ldx = _rows2d(x)
@@ -168,28 +200,46 @@ def tc_usable(x: torch.Tensor, K: int) -> bool:
     return x.dtype == torch.bfloat16 and K % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
 
 
+@_timed
 def attn_prep(qkvg: torch.Tensor, step: "StepDesc", kpool: torch.Tensor, vpool: torch.Tensor, H: int, G: int, D: int, V: int, qk_eps: float):
     _, _, ld = _rows2d(qkvg)
     _check(lib().b200seq_attn_prep(_p(qkvg), C.c_int64(ld), C.byref(step), _p(kpool), _p(vpool), H, G, D, V, C.c_float(qk_eps), _st(qkvg)))
 
 
+def attn_scratch_floats(T: int, B: int, H: int, G: int, V: int, max_keys: int) -> int:
+    """floats of work area the key-split path wants for a step of T tokens (0: the step fills the GPU without splitting)"""
+    f = lib().b200seq_attn_scratch_floats
+    f.restype = C.c_size_t
+    return int(f(T, B, H, G, V, max_keys))
+
+
+@_timed
 def attn(qkvg: torch.Tensor, step: "StepDesc", kpool: torch.Tensor, vpool: torch.Tensor, H: int, G: int, D: int, V: int, scale: float, chunk: int,
-         window: int, gated: bool, out: torch.Tensor):
+         window: int, gated: bool, out: torch.Tensor, scratch: Optional[torch.Tensor] = None):
     _, _, ld = _rows2d(qkvg)
-    assert out.is_contiguous()
+    assert out.is_contiguous() and (scratch is None or (scratch.dtype == torch.float32 and scratch.is_contiguous()))
     _check(lib().b200seq_attn(_p(qkvg), C.c_int64(ld), C.byref(step), _p(kpool), _p(vpool), H, G, D, V, C.c_float(scale), chunk, window, int(gated),
-                              _p(out), _DT[out.dtype], _st(qkvg)))
+                              _p(out), _DT[out.dtype], _p(scratch), C.c_size_t(scratch.numel() if scratch is not None else 0), _st(qkvg)))
 
 
+def ssm_scratch_floats(T: int, B: int, H: int, V: int, N: int) -> int:
+    """floats of work area the segmented (parallel over time) scan wants for a step of T tokens in B entries; 0: none needed"""
+    f = lib().b200seq_ssm_scratch_floats
+    f.restype = C.c_size_t
+    return int(f(T, B, H, V, N))
+
+
+@_timed
 def ssm_scan(proj: torch.Tensor, z0: int, dt0: int, xbc: torch.Tensor, A_log: torch.Tensor, Dp: torch.Tensor, dt_bias: torch.Tensor, state: torch.Tensor,
-             step: "StepDesc", H: int, V: int, N: int, G: int, out: torch.Tensor):
+             step: "StepDesc", H: int, V: int, N: int, G: int, out: torch.Tensor, scratch: Optional[torch.Tensor] = None):
     _, _, ldp = _rows2d(proj)
     _, _, ldx = _rows2d(xbc)
-    assert out.is_contiguous()
+    assert out.is_contiguous() and (scratch is None or (scratch.dtype == torch.float32 and scratch.is_contiguous()))
     _check(lib().b200seq_ssm_scan(_p(proj), C.c_int64(ldp), z0, dt0, _p(xbc), C.c_int64(ldx), _p(A_log), _p(Dp), _p(dt_bias), _p(state), C.byref(step),
-                                  H, V, N, G, _p(out), _st(proj)))
+                                  H, V, N, G, _p(out), _p(scratch), C.c_size_t(scratch.numel() if scratch is not None else 0), _st(proj)))
 
 
+@_timed
 def argmax(logits: torch.Tensor, ids: torch.Tensor):
     R, V = logits.shape
     assert logits.is_contiguous() and ids.dtype == torch.int32

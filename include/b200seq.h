@@ -106,15 +106,22 @@ int b200seq_linear_gated(const void* x_bf16, int64_t ldx, const void* w_il_bf16,
  * attend: token at position i sees j <= i with floor(j / chunk) == floor(i / chunk) (chunk > 0) and i - j < window (window > 0);
  *         softmax in f32, output times sigmoid(gate) when gated, written in act dtype to out [T, H*V]. */
 int b200seq_attn_prep(float* qkvg, int64_t ld, const b200seq_step* st, float* kpool, float* vpool, int H, int G, int D, int V, float qk_eps, void* stream);
+size_t b200seq_attn_scratch_floats(int T, int B, int H, int G, int V, int max_keys);
+/* scratch: f32 work area of b200seq_attn_scratch_floats(...) floats (max_keys = the most keys a token can see) or null: with it, steps of
+ * few tokens split the keys of a row among several blocks and merge the partial soft-max results. */
 int b200seq_attn(const float* qkvg, int64_t ld, const b200seq_step* st, const float* kpool, const float* vpool, int H, int G, int D, int V, float scale,
-                 int chunk, int window, int gated, void* out, int out_dtype, void* stream);
+                 int chunk, int window, int gated, void* out, int out_dtype, float* scratch, size_t scratch_floats, void* stream);
 
 /* Selective state-space recurrence, per head h (group g = h / (H / G)), state[slot][H][N][V] f32 carried per sequence:
  *   dt = softplus(dt_raw + dt_bias[h]);  S <- exp(-exp(A_log[h]) * dt) * S + dt * B x^T;  y = S^T C + D[h] * x;  out = y * silu(z)
  * proj: f32 rows (stride ldp) with z at column z0 (H*V) and dt_raw at column dt0 (H);
- * xbc:  f32 rows (stride ldx) = x (H*V) | B (G*N) | C (G*N), already convolved and activated.  out: f32 [T, H*V]. */
+ * xbc:  f32 rows (stride ldx) = x (H*V) | B (G*N) | C (G*N), already convolved and activated.  out: f32 [T, H*V].
+ * scratch: f32 work area of b200seq_ssm_scratch_floats(T, B, ...) floats or null.  With it, steps of many tokens cut every portion into
+ * segments that run in parallel (local pass, in-order combine, final pass); without it (or for short steps) each portion is one
+ * sequential walk.  Both give the same result up to rounding. */
+size_t b200seq_ssm_scratch_floats(int T, int B, int H, int V, int N);
 int b200seq_ssm_scan(const float* proj, int64_t ldp, int z0, int dt0, const float* xbc, int64_t ldx, const float* A_log, const float* Dp, const float* dt_bias,
-                     float* state, const b200seq_step* st, int H, int V, int N, int G, float* out, void* stream);
+                     float* state, const b200seq_step* st, int H, int V, int N, int G, float* out, float* scratch, size_t scratch_floats, void* stream);
 
 /* ids[r] = argmax_v logits[r][v] (first maximum) */
 int b200seq_argmax(const float* logits, int R, int V, int32_t* ids, void* stream);

@@ -181,7 +181,7 @@ def test_argmax_first_maximum(ops):
     assert ids.tolist() == [int(lg[0].argmax()), 77, 999, int(lg[3].argmax())]
 
 
-def run_attention(ops, q, k, v, gate, scale, chunk, window, eps, plan, block_size, n_pages, act=torch.float32, seed=0):
+def run_attention(ops, q, k, v, gate, scale, chunk, window, eps, plan, block_size, n_pages, act=torch.float32, seed=0, split=True):
     """feeds sequences (dict name -> (q, k, v, gate) of whole sequences) through prep + attend as the plan says; pages are taken
     from a shuffled list; returns name -> [T, H*V]"""
     names = list(q)
@@ -205,7 +205,12 @@ def run_attention(ops, q, k, v, gate, scale, chunk, window, eps, plan, block_siz
         qkvg = torch.cat(rows).contiguous().to(DEV)
         out = torch.empty(qkvg.shape[0], H * V, device=DEV, dtype=act)
         ops.attn_prep(qkvg, d, kpool, vpool, H, G, D, V, eps)
-        ops.attn(qkvg, d, kpool, vpool, H, G, D, V, scale, chunk, window, gate is not None, out)
+        scratch = None
+        if split:    # steps of few tokens deal the key tiles to several blocks and merge: the work area starts as NaN
+            keys = max(len(p) for p in pages.values()) * block_size
+            need = ops.attn_scratch_floats(qkvg.shape[0], len(step), H, G, V, min(keys, chunk or keys, window or keys))
+            scratch = torch.full((max(need, 1),), float("nan"), device=DEV)
+        ops.attn(qkvg, d, kpool, vpool, H, G, D, V, scale, chunk, window, gate is not None, out, scratch)
         o = 0
         for n, c in step:
             got[n].append(out[o:o + c].float().cpu())
@@ -346,3 +351,55 @@ def test_state_space_long_memory_shows(ops):
     got = torch.cat(outs)
     close(got, ref, 2e-5)
     assert got[-1].min() > 0.5 * got[0].max() > 0
+
+
+@pytest.mark.parametrize("H,G,N,V", [(2, 1, 16, 24), (3, 3, 40, 33), (2, 2, 128, 64), (1, 1, 200, 9)])
+def test_state_space_scan_segments_in_parallel(ops, H, G, N, V):
+    """steps of many tokens cut every portion into segments that run side by side; the result is that of one walk in order, also for
+    a portion that continues an earlier one, ends inside a segment, or shares the step with single tokens of other sequences"""
+    lens = {"a": 700, "b": 150, "c": 131}
+    inner = H * V
+    ld = 2 * inner + 2 * G * N + H
+    slot = {"a": 1, "b": 0, "c": 2}
+    data, ref = {}, {}
+    A_log, Dp, dtb = rnd(H, seed=180, scale=0.5) - 2.0, rnd(H, seed=181), rnd(H, seed=182)
+    for i, (n, T) in enumerate(lens.items()):
+        proj = rnd(T, ld, seed=183 + i)
+        xbc = rnd(T, inner + 2 * G * N, seed=190 + i)
+        data[n] = (proj, xbc)
+        y = O.ssm_recurrence(xbc[:, :inner].double().reshape(T, H, V), xbc[:, inner:inner + G * N].double().reshape(T, G, N),
+                             xbc[:, inner + G * N:].double().reshape(T, G, N), proj[:, ld - H:].double(), dtb.double(), A_log.double(), Dp.double())
+        ref[n] = y.reshape(T, inner) * O.silu(proj[:, :inner].double())
+    state = torch.full((3, H, N, V), 1e3, device=DEV)
+    plan = [[("a", 300), ("b", 1)], [("b", 1), ("a", 129), ("c", 130)], [("a", 271), ("b", 148), ("c", 1)]]
+    fed = {n: 0 for n in lens}
+    got = {n: [] for n in lens}
+    for step in plan:
+        d, keep = dev_step(ops, [(c, fed[n], slot[n], [0]) for n, c in step], 4096)
+        T = sum(c for _, c in step)
+        proj = torch.cat([data[n][0][fed[n]:fed[n] + c] for n, c in step]).to(DEV)
+        xbc = torch.cat([data[n][1][fed[n]:fed[n] + c] for n, c in step]).to(DEV)
+        need = ops.ssm_scratch_floats(T, len(step), H, V, N)
+        assert need > 0
+        scratch = torch.full((need,), float("nan"), device=DEV)
+        out = torch.empty(T, inner, device=DEV)
+        ops.ssm_scan(proj, 0, ld - H, xbc, A_log.to(DEV), Dp.to(DEV), dtb.to(DEV), state, d, H, V, N, G, out, scratch)
+        o = 0
+        for n, c in step:
+            got[n].append(out[o:o + c].cpu())
+            o += c
+            fed[n] += c
+    for n in lens:
+        close(torch.cat(got[n]), ref[n], 3e-5)
+
+
+@pytest.mark.parametrize("H,G,D,V", [(8, 2, 32, 32), (5, 5, 18, 70), (6, 1, 128, 130)])
+def test_attention_key_splits_agree_with_one_block(ops, H, G, D, V):
+    """a long prompt in one step, then single tokens: with and without the work area (keys split among blocks or not)"""
+    T = 450
+    q, k, v, gate = attention_case(T, H, G, D, V, seed=300)
+    ref = O.masked_attention(O.group_rms(q.double(), 1, 1e-6), O.group_rms(k.double(), 1, 1e-6), v.double(), 0.3, 200, 0, torch.sigmoid(gate.double())).reshape(T, -1)
+    plan = [[("a", 380)]] + [[("a", 1)] for _ in range(70)]
+    for split in (True, False):
+        got = run_attention(ops, {"a": q}, {"a": k}, {"a": v}, {"a": gate}, 0.3, 200, 0, 1e-6, plan, 16, 40, split=split)["a"]
+        close(got, ref, 2e-5)
