@@ -40,43 +40,74 @@ __global__ void embed_streams_kernel(const __nv_bfloat16* __restrict__ table, co
     }
 }
 
-// one block per row; dynamic shared memory: W floats (the collapsed vector) + 40 floats of reduction scratch
+// one block per row; dynamic shared memory: W floats (the collapsed vector) + 40 floats of reduction scratch.
+// S is a compile-time constant so that the mixing weights stay in registers; VW = 4: 16-byte accesses (W % 4 == 0).
+template <int S, int VW>
 __global__ void hc_norm_kernel(float* __restrict__ X, const float* __restrict__ y, const float* __restrict__ post, const float* __restrict__ in_w,
-                               const float* __restrict__ norm_w, int S, int W, int groups, float eps, const int32_t* __restrict__ rows,
+                               const float* __restrict__ norm_w, int W, int groups, float eps, const int32_t* __restrict__ rows,
                                void* __restrict__ out, int out_dtype) {
-    extern __shared__ float sm[];
+    extern __shared__ __align__(16) float sm[];
     float* u = sm;
     float* red = sm + W;
     const int r = blockIdx.x;
     const int64_t t = rows ? rows[r] : r;
-    float mixr[MAX_STREAMS * MAX_STREAMS], outr[MAX_STREAMS], inr[MAX_STREAMS];
+    float mixr[S * S], outr[S], inr[S];
     if (y) {
+#pragma unroll
         for (int s = 0; s < S; ++s) outr[s] = post[s];
+#pragma unroll
         for (int s = 0; s < S * S; ++s) mixr[s] = post[S + s];
     }
-    if (norm_w)
+    if (norm_w) {
+#pragma unroll
         for (int s = 0; s < S; ++s) inr[s] = in_w[s];
+    }
     float* Xt = X + t * S * W;
-    for (int i = threadIdx.x; i < W; i += blockDim.x) {
-        float xs[MAX_STREAMS];
-        for (int s = 0; s < S; ++s) xs[s] = Xt[(int64_t)s * W + i];
-        if (y) {
-            const float yv = y[t * W + i];
-            float xn[MAX_STREAMS];
-            for (int j = 0; j < S; ++j) {
-                float a = 0.f;
-                for (int s = 0; s < S; ++s) a = fmaf(mixr[s * S + j], xs[s], a);
-                xn[j] = fmaf(outr[j], yv, a);
+    for (int i = threadIdx.x * VW; i < W; i += blockDim.x * VW) {
+        float xs[S][VW];
+#pragma unroll
+        for (int s = 0; s < S; ++s) {
+            if (VW == 4) {
+                const float4 v = *reinterpret_cast<const float4*>(Xt + (int64_t)s * W + i);
+                xs[s][0] = v.x, xs[s][1 % VW] = v.y, xs[s][2 % VW] = v.z, xs[s][3 % VW] = v.w;
+            } else {
+                xs[s][0] = Xt[(int64_t)s * W + i];
             }
+        }
+        if (y) {
+            float yv[VW];
+            if (VW == 4) {
+                const float4 v = *reinterpret_cast<const float4*>(y + t * W + i);
+                yv[0] = v.x, yv[1 % VW] = v.y, yv[2 % VW] = v.z, yv[3 % VW] = v.w;
+            } else {
+                yv[0] = y[t * W + i];
+            }
+            float xn[S][VW];
+#pragma unroll
+            for (int j = 0; j < S; ++j)
+#pragma unroll
+                for (int e = 0; e < VW; ++e) {
+                    float a = 0.f;
+#pragma unroll
+                    for (int s2 = 0; s2 < S; ++s2) a = fmaf(mixr[s2 * S + j], xs[s2][e], a);
+                    xn[j][e] = fmaf(outr[j], yv[e], a);
+                }
+#pragma unroll
             for (int j = 0; j < S; ++j) {
-                xs[j] = xn[j];
-                Xt[(int64_t)j * W + i] = xn[j];
+#pragma unroll
+                for (int e = 0; e < VW; ++e) xs[j][e] = xn[j][e];
+                if (VW == 4) *reinterpret_cast<float4*>(Xt + (int64_t)j * W + i) = make_float4(xn[j][0], xn[j][1 % VW], xn[j][2 % VW], xn[j][3 % VW]);
+                else Xt[(int64_t)j * W + i] = xn[j][0];
             }
         }
         if (norm_w) {
-            float a = 0.f;
-            for (int s = 0; s < S; ++s) a = fmaf(inr[s], xs[s], a);
-            u[i] = a;
+#pragma unroll
+            for (int e = 0; e < VW; ++e) {
+                float a = 0.f;
+#pragma unroll
+                for (int s2 = 0; s2 < S; ++s2) a = fmaf(inr[s2], xs[s2][e], a);
+                u[i + e] = a;
+            }
         }
     }
     if (!norm_w) return;
@@ -157,24 +188,24 @@ __global__ void causal_conv_kernel(const float* __restrict__ x, int64_t ldx, con
     }
 }
 
+// grid (T, groups): one block per norm group of a row
 __global__ void group_rmsnorm_kernel(const float* __restrict__ x, int64_t ldx, const float* __restrict__ w, int D, int groups, float eps,
                                      void* __restrict__ out, int out_dtype) {
     __shared__ float red[40];
     const int64_t t = blockIdx.x;
-    const float* xr = x + t * ldx;
+    const int g = blockIdx.y;
     const int Dg = D / groups;
-    for (int g = 0; g < groups; ++g) {
-        float ss = 0.f;
-        for (int i = threadIdx.x; i < Dg; i += blockDim.x) {
-            const float v = xr[g * Dg + i];
-            ss = fmaf(v, v, ss);
-        }
-        ss = block_sum(ss, red);
-        const float rinv = 1.0f / sqrtf(ss / (float)Dg + eps);
-        for (int i = threadIdx.x; i < Dg; i += blockDim.x) {
-            const int k = g * Dg + i;
-            store_act(out, out_dtype, t * D + k, xr[k] * rinv * (w ? w[k] : 1.f));
-        }
+    const float* xr = x + t * ldx + (int64_t)g * Dg;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < Dg; i += blockDim.x) {
+        const float v = xr[i];
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, red);
+    const float rinv = 1.0f / sqrtf(ss / (float)Dg + eps);
+    for (int i = threadIdx.x; i < Dg; i += blockDim.x) {
+        const int k = g * Dg + i;
+        store_act(out, out_dtype, t * D + k, xr[i] * rinv * (w ? w[k] : 1.f));
     }
 }
 
@@ -258,12 +289,33 @@ int b200seq_hc_norm(float* X, const float* y, const float* post, const float* in
     if (R == 0) return 0;
     const size_t smem = ((size_t)W + 40) * sizeof(float);
     if (smem > 200 * 1024) return fail(B200SEQ_ERR_UNSUPPORTED, "hc_norm: width %d too large", W);
-    if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(hc_norm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return cuda_status(e, "hc_norm attribute");
+    const bool vec = W % 4 == 0 && (reinterpret_cast<uintptr_t>(X) & 15) == 0 && (!y || (reinterpret_cast<uintptr_t>(y) & 15) == 0);
+    const int nt = W >= 2048 ? 512 : (W >= 512 ? 256 : 128);
+    cudaError_t e = cudaSuccess;
+#define HC_LAUNCH(S_, VW_)                                                                                                                   \
+    do {                                                                                                                                     \
+        if (smem > 48 * 1024) e = cudaFuncSetAttribute(hc_norm_kernel<S_, VW_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
+        if (e == cudaSuccess)                                                                                                                \
+            hc_norm_kernel<S_, VW_><<<R, nt, smem, (cudaStream_t)stream>>>(X, y, post, in_w, norm_w, W, groups, eps, rows, out, out_dtype);  \
+    } while (0)
+#define HC_CASE(S_)                  \
+    case S_:                         \
+        if (vec) HC_LAUNCH(S_, 4);   \
+        else HC_LAUNCH(S_, 1);       \
+        break
+    switch (S) {
+        HC_CASE(1);
+        HC_CASE(2);
+        HC_CASE(3);
+        HC_CASE(4);
+        HC_CASE(5);
+        HC_CASE(6);
+        HC_CASE(7);
+        HC_CASE(8);
     }
-    const int nt = W >= 1024 ? 512 : (W >= 256 ? 256 : 128);
-    hc_norm_kernel<<<R, nt, smem, (cudaStream_t)stream>>>(X, y, post, in_w, norm_w, S, W, groups, eps, rows, out, out_dtype);
+#undef HC_CASE
+#undef HC_LAUNCH
+    if (e != cudaSuccess) return cuda_status(e, "hc_norm attribute");
     SEQ_LAUNCH_CHECK("hc_norm");
     return 0;
 }
@@ -282,7 +334,7 @@ int b200seq_causal_conv(const float* x, int64_t ldx, const float* w, const float
 int b200seq_group_rmsnorm(const float* x, int64_t ldx, const float* w, int T, int D, int groups, float eps, void* out, int out_dtype, void* stream) {
     if (!x || !out || T < 0 || D < 1 || groups < 1 || D % groups) return fail(B200SEQ_ERR_INVALID_ARG, "group_rmsnorm: bad arguments");
     if (T == 0) return 0;
-    group_rmsnorm_kernel<<<T, D / groups >= 512 ? 256 : 128, 0, (cudaStream_t)stream>>>(x, ldx, w, D, groups, eps, out, out_dtype);
+    group_rmsnorm_kernel<<<dim3(T, groups), D / groups >= 512 ? 256 : 128, 0, (cudaStream_t)stream>>>(x, ldx, w, D, groups, eps, out, out_dtype);
     SEQ_LAUNCH_CHECK("group_rmsnorm");
     return 0;
 }
@@ -301,7 +353,7 @@ int b200seq_gated_act(const float* gu, int64_t ldg, int T, int F, float limit, f
 int b200seq_argmax(const float* logits, int R, int V, int32_t* ids, void* stream) {
     if (!logits || !ids || R < 0 || V < 1) return fail(B200SEQ_ERR_INVALID_ARG, "argmax: bad arguments");
     if (R == 0) return 0;
-    argmax_kernel<<<R, 256, 0, (cudaStream_t)stream>>>(logits, V, ids);
+    argmax_kernel<<<R, V >= 4096 ? 1024 : 256, 0, (cudaStream_t)stream>>>(logits, V, ids);
     SEQ_LAUNCH_CHECK("argmax");
     return 0;
 }

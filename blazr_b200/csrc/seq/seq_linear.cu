@@ -31,12 +31,12 @@ __device__ __forceinline__ void bf16x8_to_f32(const uint4 v, float* f) {
 // MB tokens x 2 weight rows per warp.  VEC: K % 8 == 0 and 16-byte aligned rows (x rows too).
 template <typename XT, int MB, bool VEC>
 __global__ void __launch_bounds__(256) linear_rows_kernel(const XT* __restrict__ x, int64_t ldx, const __nv_bfloat16* __restrict__ w, int M, int N, int K,
-                                                          float* __restrict__ y, int64_t ldy) {
+                                                          float* __restrict__ y, int64_t ldy, int rows_per_warp) {
     const int lane = threadIdx.x & 31;
     const int warp = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    const int n0 = warp * 2;
+    const int n0 = warp * rows_per_warp;
     if (n0 >= N) return;
-    const bool two = n0 + 1 < N;
+    const bool two = rows_per_warp == 2 && n0 + 1 < N;
     const __nv_bfloat16* w0 = w + (int64_t)n0 * K;
     const __nv_bfloat16* w1 = w + (int64_t)(two ? n0 + 1 : n0) * K;
     for (int m0 = 0; m0 < M; m0 += MB) {
@@ -144,17 +144,18 @@ template <typename XT>
 static void launch_rows(const XT* x, int64_t ldx, const __nv_bfloat16* w, int M, int N, int K, float* y, int64_t ldy, cudaStream_t st) {
     const bool vec = K % 8 == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
                      (ldx * (int64_t)sizeof(XT)) % 16 == 0;
-    const int warps = (N + 1) / 2;
+    const int rpw = (N + 15) / 16 >= 4 * 148 ? 2 : 1;   // few rows: one per warp, so that every SM streams weights
+    const int warps = (N + rpw - 1) / rpw;
     const int blocks = (warps + 7) / 8;
     if (M <= 1) {
-        if (vec) linear_rows_kernel<XT, 1, true><<<blocks, 256, 0, st>>>(x, ldx, w, M, N, K, y, ldy);
-        else linear_rows_kernel<XT, 1, false><<<blocks, 256, 0, st>>>(x, ldx, w, M, N, K, y, ldy);
+        if (vec) linear_rows_kernel<XT, 1, true><<<blocks, 256, 0, st>>>(x, ldx, w, M, N, K, y, ldy, rpw);
+        else linear_rows_kernel<XT, 1, false><<<blocks, 256, 0, st>>>(x, ldx, w, M, N, K, y, ldy, rpw);
     } else if (M <= 2) {
-        if (vec) linear_rows_kernel<XT, 2, true><<<blocks, 256, 0, st>>>(x, ldx, w, M, N, K, y, ldy);
-        else linear_rows_kernel<XT, 2, false><<<blocks, 256, 0, st>>>(x, ldx, w, M, N, K, y, ldy);
+        if (vec) linear_rows_kernel<XT, 2, true><<<blocks, 256, 0, st>>>(x, ldx, w, M, N, K, y, ldy, rpw);
+        else linear_rows_kernel<XT, 2, false><<<blocks, 256, 0, st>>>(x, ldx, w, M, N, K, y, ldy, rpw);
     } else {
-        if (vec) linear_rows_kernel<XT, 4, true><<<blocks, 256, 0, st>>>(x, ldx, w, M, N, K, y, ldy);
-        else linear_rows_kernel<XT, 4, false><<<blocks, 256, 0, st>>>(x, ldx, w, M, N, K, y, ldy);
+        if (vec) linear_rows_kernel<XT, 4, true><<<blocks, 256, 0, st>>>(x, ldx, w, M, N, K, y, ldy, rpw);
+        else linear_rows_kernel<XT, 4, false><<<blocks, 256, 0, st>>>(x, ldx, w, M, N, K, y, ldy, rpw);
     }
 }
 

@@ -293,7 +293,28 @@ def bench_decoder(size: str, pk, S: int = 4096, ctx: int = 1024, batches=(1, 4),
     roof = max(fl / (pk["bf16_tflops"] * 1e12), (gu.w.canonical_bytes + S * gu.w.K * 4 + S * gu.w.N * 4) / (pk["hbm_gbs"] * 1e9)) * 1e6
     kern.append({"op": f"dequant GEMM gate|up M={S} N={gu.w.N} K={gu.w.K} (staging + tcgen05)", "us": round(us, 1), "roof_us": round(roof, 1), "frac_of_roofline": round(roof / us, 4),
                  "bound": "tensor"})
-    del d, x, y, ws
+    # residual add + RMS norm at M = S (the like kernel of the stream update + grouped norm): reads h, delta, writes h', normed
+    Hd = cfg.hidden
+    hin, dl, hout, xn = (torch.randn((S, Hd), device=client.device) for _ in range(4))
+    L_, P_ = ops.lib(), (lambda t_: C.c_void_p(t_.data_ptr()))
+    st_ = ops._stream_ptr(client.device)
+
+    def norm_once():
+        ops._check(L_.b200q_add_rmsnorm_quant(P_(hin), P_(dl), P_(hout), P_(lay["attn_norm"]), C.c_float(cfg.eps), C.c_int64(Hd), C.c_int64(S), None, P_(xn), st_))
+
+    for _ in range(3):
+        norm_once()
+    e0, e1 = _events()
+    e0.record()
+    for _ in range(10):
+        norm_once()
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / 10
+    by = 4 * S * Hd * 4
+    kern.append({"op": f"residual add + RMS norm M={S} W={Hd}", "us": round(us, 1), "roof_us": round(by / (pk['hbm_gbs'] * 1e9) * 1e6, 1),
+                 "frac_of_roofline": round(by / (pk["hbm_gbs"] * 1e9) * 1e6 / us, 4), "bound": "hbm"})
+    del d, x, y, ws, hin, dl, hout, xn
     torch.cuda.empty_cache()
     out["decode"] = []
     for B in batches:

@@ -275,3 +275,29 @@ def test_trace_replay_command(cases, tmp_path):
     g1 = np.fromfile(os.path.join(out, "1.f32"), dtype="<f4").reshape(1, V)
     g2 = np.fromfile(os.path.join(out, "2.f32"), dtype="<f4").reshape(1, V)
     assert err(g0, ref[19:20]) < TOL32 and err(g1, ref[2:3]) < TOL32 and err(g2, ref[29:30]) < TOL32
+
+
+CONFIGS["long"] = config([ssm(heads=3, vdim=24, state=40, groups=1, norm_groups=3, conv=4), att(dim=24, vdim=40, heads=6, kv=2, size=150, scale=0.2, ff=56),
+                          ssm(heads=2, vdim=16, state=130, groups=2, norm_groups=1, conv=2, ff=32)], vocab=77, width=64, streams=3, groups=2, taps=3)
+
+
+def test_long_portions_next_to_single_tokens(cases):
+    """portions of hundreds of tokens (the recurrence runs as parallel segments, attention as query tiles over many key tiles) in the
+    same steps as single tokens of another request; then both decode side by side"""
+    c = cases("long")
+    a, b = toks(520, c.cfg["vocab"], 20), toks(160, c.cfg["vocab"], 21)
+    ra, rb = c.ref(a), c.ref(b)
+    eng = c.engine(max_tokens=720, max_seqs=2)
+    got = eng.run_entries([{"id": "b", "tokens": b[:3], "want": [2]}], [])
+    assert err(got, rb[2:3]) < TOL32
+    got = eng.run_entries([{"id": "a", "tokens": a[:300], "want": [0, 127, 128, 149, 150, 299]}, {"id": "b", "tokens": [b[3]], "want": [0]}], [])
+    assert err(got, torch.cat([ra[[0, 127, 128, 149, 150, 299]], rb[3:4]])) < TOL32
+    got = eng.run_entries([{"id": "b", "tokens": b[4:135], "want": [0, 130]}, {"id": "a", "tokens": a[300:470], "want": [0, 1, 169]}], [])
+    assert err(got, torch.cat([rb[[4, 134]], ra[[300, 301, 469]]])) < TOL32
+    for i in range(25):
+        got = eng.run_entries([{"id": "a", "tokens": [a[470 + i]], "want": [0]}, {"id": "b", "tokens": [b[135 + i]], "want": [0]}], [])
+        assert err(got, torch.cat([ra[470 + i:471 + i], rb[135 + i:136 + i]])) < TOL32, f"decoded token {i}"
+    got = eng.run_entries([{"id": "a", "tokens": a[495:520], "want": [24]}], ["a", "b"])
+    assert err(got, ra[519:520]) < TOL32
+    from blazr_b200 import seqops
+    assert seqops.error_flags() == 0
