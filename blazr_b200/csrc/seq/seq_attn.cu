@@ -96,7 +96,7 @@ __device__ __forceinline__ float dot4(const float4 a, const float4 b, float acc)
 }
 
 template <int RT, int VPT>
-__global__ void __launch_bounds__(AT_NT) attn_tile_kernel(const AttnArgs a, const b200seq_step st) {
+__global__ void __launch_bounds__(AT_NT, (RT == 4 && VPT == 4) ? 3 : 1) attn_tile_kernel(const AttnArgs a, const b200seq_step st) {
     extern __shared__ __align__(16) float sm[];
     constexpr int RQ = 16 * RT, VS = 16 * VPT, PS = AT_KT + 4;
     const int D = a.D, V = a.V, H = a.H, G = a.G;

@@ -125,66 +125,105 @@ __global__ void hc_norm_kernel(float* __restrict__ X, const float* __restrict__ 
     }
 }
 
-// thread = one channel, blockIdx.y = a tile of CONV_TILE consecutive token rows.  The first taps-1 tokens of an entry read the carried
-// state; they and the state's rewrite belong to the thread that meets the entry's first token, so no other thread touches that state.
+// thread = VW neighbouring channels (VW = 4: 16-byte accesses), blockIdx.y = a tile of CONV_TILE consecutive token rows.  The first
+// taps-1 tokens of an entry read the carried state; they and the state's rewrite belong to the thread that meets the entry's first
+// token, so no other thread touches that state.
 constexpr int CONV_TILE = 16;
+template <int VW>
 __global__ void causal_conv_kernel(const float* __restrict__ x, int64_t ldx, const float* __restrict__ w, const float* __restrict__ bias,
                                    float* __restrict__ state, b200seq_step st, int C, int taps, int mode, void* __restrict__ out, int out_dtype,
                                    int64_t ldo) {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= C) return;
-    float wr[MAX_TAPS];
+    const int c0 = (blockIdx.x * blockDim.x + threadIdx.x) * VW;
+    if (c0 >= C) return;
+    float wr[VW][MAX_TAPS], b[VW];
 #pragma unroll
-    for (int j = 0; j < MAX_TAPS; ++j) wr[j] = j < taps ? w[(int64_t)c * taps + j] : 0.f;
-    const float b = bias ? bias[c] : 0.f;
+    for (int e = 0; e < VW; ++e) {
+#pragma unroll
+        for (int j = 0; j < MAX_TAPS; ++j) wr[e][j] = j < taps ? w[(int64_t)(c0 + e) * taps + j] : 0.f;
+        b[e] = bias ? bias[c0 + e] : 0.f;
+    }
     const int hist = taps - 1;
-    auto emit = [&](int64_t row, float acc, float xin) {
-        float v = acc + b;
+    auto finish = [&](float acc, float bb, float xin) {
+        float v = acc + bb;
         if (mode & B200SEQ_CONV_SILU) v = siluf_acc(v);
         if (mode & B200SEQ_CONV_RESIDUAL) v = xin + v;
-        store_act(out, out_dtype, row * ldo + c, v);
+        return v;
     };
     const int t0 = blockIdx.y * CONV_TILE, t1 = min(t0 + CONV_TILE, st.T);
     for (int t = t0; t < t1; ++t) {
-        const int e = st.tok_ent[t];
-        const int s0 = st.ent_start[e];
+        const int en = st.tok_ent[t];
+        const int s0 = st.ent_start[en];
         const int i = t - s0;
         if (i < hist) {
             if (i != 0) continue;
-            const int len = st.ent_start[e + 1] - s0;
-            const int64_t sbase = (int64_t)st.ent_slot[e] * hist * C + c;
-            const bool fresh = st.ent_pos0[e] == 0;
-            float old[MAX_TAPS];
+            const int len = st.ent_start[en + 1] - s0;
+            const bool fresh = st.ent_pos0[en] == 0;
+            const int n_own = min(hist, len);
 #pragma unroll
-            for (int j = 0; j < MAX_TAPS; ++j) old[j] = (j < hist && !fresh) ? state[sbase + (int64_t)j * C] : 0.f;
-            // input at entry-relative index idx (negative = carried)
-            auto src = [&](int idx) -> float {
-                if (idx >= 0) return x[(int64_t)(s0 + idx) * ldx + c];
-                float v = 0.f;
+            for (int e = 0; e < VW; ++e) {
+                const int c = c0 + e;
+                const int64_t sbase = (int64_t)st.ent_slot[en] * hist * C + c;
+                float old[MAX_TAPS];
+#pragma unroll
+                for (int j = 0; j < MAX_TAPS; ++j) old[j] = (j < hist && !fresh) ? state[sbase + (int64_t)j * C] : 0.f;
+                // input at entry-relative index idx (negative = carried)
+                auto src = [&](int idx) -> float {
+                    if (idx >= 0) return x[(int64_t)(s0 + idx) * ldx + c];
+                    float v = 0.f;
+#pragma unroll
+                    for (int j = 0; j < MAX_TAPS; ++j)
+                        if (j == hist + idx) v = old[j];
+                    return v;
+                };
+                for (int ii = 0; ii < n_own; ++ii) {
+                    float acc = 0.f;
+#pragma unroll
+                    for (int j = 0; j < MAX_TAPS; ++j)
+                        if (j < taps) acc = fmaf(wr[e][j], src(ii - hist + j), acc);
+                    store_act(out, out_dtype, (int64_t)(s0 + ii) * ldo + c, finish(acc, b[e], x[(int64_t)(s0 + ii) * ldx + c]));
+                }
+                float nv[MAX_TAPS];
+#pragma unroll
+                for (int j = 0; j < MAX_TAPS; ++j) nv[j] = j < hist ? src(len - hist + j) : 0.f;
 #pragma unroll
                 for (int j = 0; j < MAX_TAPS; ++j)
-                    if (j == hist + idx) v = old[j];
-                return v;
-            };
-            const int n_own = min(hist, len);
-            for (int ii = 0; ii < n_own; ++ii) {
-                float acc = 0.f;
-                for (int j = 0; j < taps; ++j) acc = fmaf(wr[j], src(ii - hist + j), acc);
-                emit(s0 + ii, acc, x[(int64_t)(s0 + ii) * ldx + c]);
+                    if (j < hist) state[sbase + (int64_t)j * C] = nv[j];
             }
-            float nv[MAX_TAPS];
-#pragma unroll
-            for (int j = 0; j < MAX_TAPS; ++j) nv[j] = j < hist ? src(len - hist + j) : 0.f;
-#pragma unroll
-            for (int j = 0; j < MAX_TAPS; ++j)
-                if (j < hist) state[sbase + (int64_t)j * C] = nv[j];
             continue;
         }
-        float acc = 0.f;
+        float acc[VW], cur[VW];
 #pragma unroll
-        for (int j = 0; j < MAX_TAPS; ++j)
-            if (j < taps) acc = fmaf(wr[j], x[(int64_t)(t - hist + j) * ldx + c], acc);
-        emit(t, acc, x[(int64_t)t * ldx + c]);
+        for (int e = 0; e < VW; ++e) acc[e] = 0.f, cur[e] = 0.f;
+#pragma unroll
+        for (int j = 0; j < MAX_TAPS; ++j) {
+            if (j < taps) {
+                const float* xp = x + (int64_t)(t - hist + j) * ldx + c0;
+                if (VW == 4) {
+                    const float4 v = *reinterpret_cast<const float4*>(xp);
+                    cur[0] = v.x, cur[1 % VW] = v.y, cur[2 % VW] = v.z, cur[3 % VW] = v.w;
+                } else {
+                    cur[0] = xp[0];
+                }
+#pragma unroll
+                for (int e = 0; e < VW; ++e) acc[e] = fmaf(wr[e][j], cur[e], acc[e]);
+            }
+        }
+        // cur holds the row's own input (the last tap)
+        float v[VW];
+#pragma unroll
+        for (int e = 0; e < VW; ++e) v[e] = finish(acc[e], b[e], cur[e]);
+        if (VW == 4) {
+            if (out_dtype == B200SEQ_F32) {
+                *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + (int64_t)t * ldo + c0) = make_float4(v[0], v[1 % VW], v[2 % VW], v[3 % VW]);
+            } else {
+                __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1 % VW]), hi = __floats2bfloat162_rn(v[2 % VW], v[3 % VW]);
+                uint2 pk;
+                pk.x = *reinterpret_cast<uint32_t*>(&lo), pk.y = *reinterpret_cast<uint32_t*>(&hi);
+                *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(out) + (int64_t)t * ldo + c0) = pk;
+            }
+        } else {
+            store_act(out, out_dtype, (int64_t)t * ldo + c0, v[0]);
+        }
     }
 }
 
@@ -325,8 +364,14 @@ int b200seq_causal_conv(const float* x, int64_t ldx, const float* w, const float
     if (!x || !w || !st || !out || C < 1 || taps < 1 || taps > MAX_TAPS || (taps > 1 && !state)) return fail(B200SEQ_ERR_INVALID_ARG, "causal_conv: bad arguments (1 <= taps <= %d)", MAX_TAPS);
     if (out_dtype != B200SEQ_F32 && out_dtype != B200SEQ_BF16) return fail(B200SEQ_ERR_INVALID_ARG, "causal_conv: output dtype");
     if (st->T == 0) return 0;
-    dim3 grid((C + 127) / 128, (st->T + CONV_TILE - 1) / CONV_TILE);
-    causal_conv_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(x, ldx, w, bias, state, *st, C, taps, mode, out, out_dtype, ldo);
+    const bool vec = C % 4 == 0 && ldx % 4 == 0 && ldo % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+    if (vec) {
+        dim3 grid((C / 4 + 127) / 128, (st->T + CONV_TILE - 1) / CONV_TILE);
+        causal_conv_kernel<4><<<grid, 128, 0, (cudaStream_t)stream>>>(x, ldx, w, bias, state, *st, C, taps, mode, out, out_dtype, ldo);
+    } else {
+        dim3 grid((C + 127) / 128, (st->T + CONV_TILE - 1) / CONV_TILE);
+        causal_conv_kernel<1><<<grid, 128, 0, (cudaStream_t)stream>>>(x, ldx, w, bias, state, *st, C, taps, mode, out, out_dtype, ldo);
+    }
     SEQ_LAUNCH_CHECK("causal_conv");
     return 0;
 }
