@@ -42,10 +42,18 @@ __global__ void embed_streams_kernel(const __nv_bfloat16* __restrict__ table, co
 
 // one block per row; dynamic shared memory: W floats (the collapsed vector) + 40 floats of reduction scratch.
 // S is a compile-time constant so that the mixing weights stay in registers; VW = 4: 16-byte accesses (W % 4 == 0).
+// With conv_w (steps in which every entry brings ONE token, rows == null): the carried convolution of the sublayer's input follows in
+// the same kernel, out = h + conv(h) with the taps-1 earlier h of the sequence read from and shifted in conv_state[slot][taps-1][W].
+struct HcConv {
+    const float* w;      // [W, taps] or null
+    float* state;
+    const int32_t *ent_slot, *ent_pos0;
+    int taps;
+};
 template <int S, int VW>
 __global__ void hc_norm_kernel(float* __restrict__ X, const float* __restrict__ y, const float* __restrict__ post, const float* __restrict__ in_w,
                                const float* __restrict__ norm_w, int W, int groups, float eps, const int32_t* __restrict__ rows,
-                               void* __restrict__ out, int out_dtype) {
+                               void* __restrict__ out, int out_dtype, const HcConv cv) {
     extern __shared__ __align__(16) float sm[];
     float* u = sm;
     float* red = sm + W;
@@ -121,7 +129,27 @@ __global__ void hc_norm_kernel(float* __restrict__ X, const float* __restrict__ 
         }
         ss = block_sum(ss, red);
         const float rinv = 1.0f / sqrtf(ss / (float)Wg + eps);
-        for (int i = threadIdx.x; i < Wg; i += blockDim.x) store_act(out, out_dtype, (int64_t)r * W + g * Wg + i, u[g * Wg + i] * rinv * norm_w[g * Wg + i]);
+        if (!cv.w) {
+            for (int i = threadIdx.x; i < Wg; i += blockDim.x) store_act(out, out_dtype, (int64_t)r * W + g * Wg + i, u[g * Wg + i] * rinv * norm_w[g * Wg + i]);
+            continue;
+        }
+        const int hist = cv.taps - 1;
+        const bool fresh = cv.ent_pos0[r] == 0;
+        float* sp = cv.state + (int64_t)cv.ent_slot[r] * hist * W;
+        for (int i = threadIdx.x; i < Wg; i += blockDim.x) {
+            const int c = g * Wg + i;
+            const float hv = u[c] * rinv * norm_w[c];
+            const float* wc = cv.w + (int64_t)c * cv.taps;
+            float acc = wc[hist] * hv;
+            float next = hv;                           // what row j receives: the old row j + 1 (the new h for the last row)
+            for (int j = hist - 1; j >= 0; --j) {
+                const float old = fresh ? 0.f : sp[(int64_t)j * W + c];
+                acc = fmaf(wc[j], old, acc);
+                sp[(int64_t)j * W + c] = next;
+                next = old;
+            }
+            store_act(out, out_dtype, (int64_t)r * W + c, hv + acc);
+        }
     }
 }
 
@@ -321,8 +349,23 @@ int b200seq_embed_streams(const void* table, const int32_t* ids, float scale, in
     return 0;
 }
 
+static int hc_norm_launch(float* X, const float* y, const float* post, const float* in_w, const float* norm_w, int S, int W, int groups, float eps,
+                          const int32_t* rows, int R, void* out, int out_dtype, const HcConv cv, void* stream);
+
 int b200seq_hc_norm(float* X, const float* y, const float* post, const float* in_w, const float* norm_w, int S, int W, int groups, float eps,
                     const int32_t* rows, int R, void* out, int out_dtype, void* stream) {
+    return hc_norm_launch(X, y, post, in_w, norm_w, S, W, groups, eps, rows, R, out, out_dtype, HcConv{nullptr, nullptr, nullptr, nullptr, 1}, stream);
+}
+
+int b200seq_hc_norm_conv(float* X, const float* y, const float* post, const float* in_w, const float* norm_w, int S, int W, int groups, float eps,
+                         const float* conv_w, float* conv_state, const b200seq_step* st, int taps, void* out, int out_dtype, void* stream) {
+    if (!conv_w || !st || !norm_w || taps < 1 || taps > MAX_TAPS || (taps > 1 && !conv_state)) return fail(B200SEQ_ERR_INVALID_ARG, "hc_norm_conv: bad arguments");
+    if (st->T != st->B) return fail(B200SEQ_ERR_INVALID_ARG, "hc_norm_conv: every entry of the step must bring exactly one token");
+    return hc_norm_launch(X, y, post, in_w, norm_w, S, W, groups, eps, nullptr, st->T, out, out_dtype, HcConv{conv_w, conv_state, st->ent_slot, st->ent_pos0, taps}, stream);
+}
+
+static int hc_norm_launch(float* X, const float* y, const float* post, const float* in_w, const float* norm_w, int S, int W, int groups, float eps,
+                          const int32_t* rows, int R, void* out, int out_dtype, const HcConv cv, void* stream) {
     if (!X || S < 1 || S > MAX_STREAMS || W < 1 || R < 0) return fail(B200SEQ_ERR_INVALID_ARG, "hc_norm: bad arguments");
     if ((y && !post) || (norm_w && (!in_w || !out || groups < 1 || W % groups))) return fail(B200SEQ_ERR_INVALID_ARG, "hc_norm: missing parameters or width not divisible by groups");
     if (R == 0) return 0;
@@ -335,7 +378,7 @@ int b200seq_hc_norm(float* X, const float* y, const float* post, const float* in
     do {                                                                                                                                     \
         if (smem > 48 * 1024) e = cudaFuncSetAttribute(hc_norm_kernel<S_, VW_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
         if (e == cudaSuccess)                                                                                                                \
-            hc_norm_kernel<S_, VW_><<<R, nt, smem, (cudaStream_t)stream>>>(X, y, post, in_w, norm_w, W, groups, eps, rows, out, out_dtype);  \
+            hc_norm_kernel<S_, VW_><<<R, nt, smem, (cudaStream_t)stream>>>(X, y, post, in_w, norm_w, W, groups, eps, rows, out, out_dtype, cv);  \
     } while (0)
 #define HC_CASE(S_)                  \
     case S_:                         \

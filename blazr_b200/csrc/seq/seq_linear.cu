@@ -29,9 +29,17 @@ __device__ __forceinline__ void bf16x8_to_f32(const uint4 v, float* f) {
 }
 
 // MB tokens x 2 weight rows per warp.  VEC: K % 8 == 0 and 16-byte aligned rows (x rows too).
+// gated epilogue of a stacked gate|up weight with alternating rows: a warp's two rows are (gate j, up j); act[m][j] is written instead of y
+struct GateEpi {
+    void* out;       // null: plain product to y
+    int out_dtype;
+    int64_t ldo;
+    float limit, alpha, shift;
+};
+
 template <typename XT, int MB, bool VEC>
 __global__ void __launch_bounds__(256) linear_rows_kernel(const XT* __restrict__ x, int64_t ldx, const __nv_bfloat16* __restrict__ w, int M, int N, int K,
-                                                          float* __restrict__ y, int64_t ldy, int rows_per_warp) {
+                                                          float* __restrict__ y, int64_t ldy, int rows_per_warp, const GateEpi ge) {
     const int lane = threadIdx.x & 31;
     const int warp = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int n0 = warp * rows_per_warp;
@@ -84,8 +92,14 @@ __global__ void __launch_bounds__(256) linear_rows_kernel(const XT* __restrict__
         for (int m = 0; m < MB; ++m) {
             const float s0 = warp_sum(acc0[m]), s1 = warp_sum(acc1[m]);
             if (lane == 0 && m0 + m < M) {
-                y[(int64_t)(m0 + m) * ldy + n0] = s0;
-                if (two) y[(int64_t)(m0 + m) * ldy + n0 + 1] = s1;
+                if (ge.out) {
+                    const float g = fminf(s0, ge.limit);
+                    const float u = fminf(fmaxf(s1, -ge.limit), ge.limit);
+                    store_act(ge.out, ge.out_dtype, (int64_t)(m0 + m) * ge.ldo + (n0 >> 1), g * sigmoidf_acc(ge.alpha * g) * (u + ge.shift));
+                } else {
+                    y[(int64_t)(m0 + m) * ldy + n0] = s0;
+                    if (two) y[(int64_t)(m0 + m) * ldy + n0 + 1] = s1;
+                }
             }
         }
     }
@@ -141,21 +155,22 @@ __global__ void __launch_bounds__(256) linear_tiled_kernel(const XT* __restrict_
 }
 
 template <typename XT>
-static void launch_rows(const XT* x, int64_t ldx, const __nv_bfloat16* w, int M, int N, int K, float* y, int64_t ldy, cudaStream_t st) {
+static void launch_rows(const XT* x, int64_t ldx, const __nv_bfloat16* w, int M, int N, int K, float* y, int64_t ldy, cudaStream_t st,
+                        const GateEpi ge = GateEpi{nullptr, 0, 0, 0.f, 0.f, 0.f}) {
     const bool vec = K % 8 == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
                      (ldx * (int64_t)sizeof(XT)) % 16 == 0;
-    const int rpw = (N + 15) / 16 >= 4 * 148 ? 2 : 1;   // few rows: one per warp, so that every SM streams weights
+    const int rpw = (ge.out || (N + 15) / 16 >= 4 * 148) ? 2 : 1;   // few rows: one per warp, so that every SM streams weights
     const int warps = (N + rpw - 1) / rpw;
     const int blocks = (warps + 7) / 8;
     if (M <= 1) {
-        if (vec) linear_rows_kernel<XT, 1, true><<<blocks, 256, 0, st>>>(x, ldx, w, M, N, K, y, ldy, rpw);
-        else linear_rows_kernel<XT, 1, false><<<blocks, 256, 0, st>>>(x, ldx, w, M, N, K, y, ldy, rpw);
+        if (vec) linear_rows_kernel<XT, 1, true><<<blocks, 256, 0, st>>>(x, ldx, w, M, N, K, y, ldy, rpw, ge);
+        else linear_rows_kernel<XT, 1, false><<<blocks, 256, 0, st>>>(x, ldx, w, M, N, K, y, ldy, rpw, ge);
     } else if (M <= 2) {
-        if (vec) linear_rows_kernel<XT, 2, true><<<blocks, 256, 0, st>>>(x, ldx, w, M, N, K, y, ldy, rpw);
-        else linear_rows_kernel<XT, 2, false><<<blocks, 256, 0, st>>>(x, ldx, w, M, N, K, y, ldy, rpw);
+        if (vec) linear_rows_kernel<XT, 2, true><<<blocks, 256, 0, st>>>(x, ldx, w, M, N, K, y, ldy, rpw, ge);
+        else linear_rows_kernel<XT, 2, false><<<blocks, 256, 0, st>>>(x, ldx, w, M, N, K, y, ldy, rpw, ge);
     } else {
-        if (vec) linear_rows_kernel<XT, 4, true><<<blocks, 256, 0, st>>>(x, ldx, w, M, N, K, y, ldy, rpw);
-        else linear_rows_kernel<XT, 4, false><<<blocks, 256, 0, st>>>(x, ldx, w, M, N, K, y, ldy, rpw);
+        if (vec) linear_rows_kernel<XT, 4, true><<<blocks, 256, 0, st>>>(x, ldx, w, M, N, K, y, ldy, rpw, ge);
+        else linear_rows_kernel<XT, 4, false><<<blocks, 256, 0, st>>>(x, ldx, w, M, N, K, y, ldy, rpw, ge);
     }
 }
 
@@ -191,11 +206,19 @@ extern "C" int b200seq_linear(const void* x, int x_dtype, int64_t ldx, const voi
     return 0;
 }
 
-extern "C" int b200seq_linear_gated(const void* x, int64_t ldx, const void* w, int M, int F, int K, float limit, float alpha, float up_shift, void* out,
-                                    int out_dtype, int64_t ldo, void* stream) {
+extern "C" int b200seq_linear_gated(const void* x, int x_dtype, int64_t ldx, const void* w, int M, int F, int K, float limit, float alpha, float up_shift,
+                                    void* out, int out_dtype, int64_t ldo, void* stream) {
     if (!x || !w || !out || M < 0 || F < 1 || K < 1 || ldx < K || ldo < F) return fail(B200SEQ_ERR_INVALID_ARG, "linear_gated: bad arguments");
     if (out_dtype != B200SEQ_F32 && out_dtype != B200SEQ_BF16) return fail(B200SEQ_ERR_INVALID_ARG, "linear_gated: output dtype");
+    if (x_dtype != B200SEQ_F32 && x_dtype != B200SEQ_BF16) return fail(B200SEQ_ERR_INVALID_ARG, "linear_gated: activation dtype");
     if (M == 0) return 0;
-    if (!linear_tc_usable(B200SEQ_BF16, ldx, M, 2 * F, K, x, w)) return fail(B200SEQ_ERR_UNSUPPORTED, "linear_gated: needs K %% 8 == 0 and 16-byte aligned rows");
+    if (M <= 8) {   // few tokens: the weight-streaming kernel, a warp's two rows are one (gate, up) pair
+        const GateEpi ge{out, out_dtype, ldo, limit, alpha, up_shift};
+        if (x_dtype == B200SEQ_F32) launch_rows((const float*)x, ldx, (const __nv_bfloat16*)w, M, 2 * F, K, nullptr, 0, (cudaStream_t)stream, ge);
+        else launch_rows((const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w, M, 2 * F, K, nullptr, 0, (cudaStream_t)stream, ge);
+        SEQ_LAUNCH_CHECK("linear_gated rows");
+        return 0;
+    }
+    if (!linear_tc_usable(x_dtype, ldx, M, 2 * F, K, x, w)) return fail(B200SEQ_ERR_UNSUPPORTED, "linear_gated: more than 8 rows need bf16 activations, K %% 8 == 0 and 16-byte aligned rows");
     return launch_linear_tc_gated(x, ldx, w, M, F, K, limit, alpha, up_shift, out, out_dtype, ldo, (cudaStream_t)stream);
 }

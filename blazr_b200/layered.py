@@ -314,8 +314,11 @@ class LayeredModel:
         for L in self.layers:
             ls: LayerSpec = L["spec"]
             for q in ((1, 2) if ls.ff is not None else (1,)):
-                ops.hc_norm(X, y_prev, post_prev, L[f"hc{q}_in"], L[f"norm{q}"], cfg.norm_groups, cfg.eps, h)
-                ops.causal_conv(h, L[f"canon{q}"], None, L[f"canon{q}_state"], st, ops.CONV_RESIDUAL, a)
+                if T == B:      # one token per entry: the convolution's history is all in the carried state -> one kernel
+                    ops.hc_norm_conv(X, y_prev, post_prev, L[f"hc{q}_in"], L[f"norm{q}"], cfg.norm_groups, cfg.eps, L[f"canon{q}"], L[f"canon{q}_state"], st, a)
+                else:
+                    ops.hc_norm(X, y_prev, post_prev, L[f"hc{q}_in"], L[f"norm{q}"], cfg.norm_groups, cfg.eps, h)
+                    ops.causal_conv(h, L[f"canon{q}"], None, L[f"canon{q}_state"], st, ops.CONV_RESIDUAL, a)
                 if q == 2:
                     self._dense_ff(L, ls.ff, ws, T, a, y)
                 elif ls.kind == "attention":
@@ -358,7 +361,7 @@ class LayeredModel:
 
     def _dense_ff(self, L, f: DenseFfSpec, ws: _Workspace, T: int, a: torch.Tensor, y: torch.Tensor) -> None:
         act = ws.inner_a.view(-1)[:T * f.ff].view(T, f.ff)
-        if T >= seqops.TC_MIN_ROWS and seqops.tc_usable(a, a.shape[1]):     # projection and activation in one tensor-core kernel
+        if T <= 8 or (T >= seqops.TC_MIN_ROWS and seqops.tc_usable(a, a.shape[1])):     # projection and activation in one kernel
             seqops.linear_gated(a, L["w_gu"], f.limit, f.alpha, f.up_shift, act)
         else:
             gu = ws.proj[:T, :2 * f.ff]

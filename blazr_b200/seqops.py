@@ -27,7 +27,7 @@ PATH_AUTO, PATH_ROWS, PATH_TILED, PATH_TC = 0, 1, 2, 3
 TC_MIN_ROWS = 32   # b200seq_linear's automatic choice takes the tensor-core path from this many rows
 _DT = {torch.float32: F32, torch.bfloat16: BF16}
 
-EXPORTS = ["b200seq_last_error", "b200seq_version", "b200seq_launch_count", "b200seq_error_flags", "b200seq_embed_streams", "b200seq_hc_norm",
+EXPORTS = ["b200seq_last_error", "b200seq_version", "b200seq_launch_count", "b200seq_error_flags", "b200seq_embed_streams", "b200seq_hc_norm", "b200seq_hc_norm_conv",
            "b200seq_causal_conv", "b200seq_group_rmsnorm", "b200seq_gated_act", "b200seq_linear", "b200seq_linear_gated", "b200seq_attn_prep", "b200seq_attn", "b200seq_attn_scratch_floats",
            "b200seq_ssm_scan", "b200seq_ssm_scratch_floats", "b200seq_argmax"]
 
@@ -155,6 +155,15 @@ def hc_norm(X: torch.Tensor, y: Optional[torch.Tensor], post: Optional[torch.Ten
 
 
 @_timed
+def hc_norm_conv(X: torch.Tensor, y: Optional[torch.Tensor], post: Optional[torch.Tensor], in_w: torch.Tensor, norm_w: torch.Tensor, groups: int, eps: float,
+                 conv_w: torch.Tensor, conv_state: torch.Tensor, step: "StepDesc", out: torch.Tensor):
+    """hc_norm followed by the residual carried convolution in one kernel; only for steps in which every entry brings one token"""
+    T, S, W = X.shape
+    _check(lib().b200seq_hc_norm_conv(_p(X), _p(y), _p(post), _p(in_w), _p(norm_w), S, W, groups, C.c_float(eps), _p(conv_w), _p(conv_state), C.byref(step),
+                                      conv_w.shape[1], _p(out), _DT[out.dtype], _st(X)))
+
+
+@_timed
 def causal_conv(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], state: Optional[torch.Tensor], step: "StepDesc", mode: int, out: torch.Tensor):
     T, Cn, ldx = _rows2d(x)
     _, _, ldo = _rows2d(out)
@@ -187,11 +196,12 @@ def linear(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, path: int = PATH_A
 
 @_timed
 def linear_gated(x: torch.Tensor, w_il: torch.Tensor, limit: float, alpha: float, up_shift: float, out: torch.Tensor):
-    """out[M, F] = gated_act(x . w_il^T); w_il bf16 [2F, K] with alternating gate / up rows (tensor-core path only)"""
+    """out[M, F] = gated_act(x . w_il^T); w_il bf16 [2F, K] with alternating gate / up rows (up to 8 rows: any activation type;
+    more: the tensor-core path, bf16 activations only)"""
     M, K, ldx = _rows2d(x)
     _, F, ldo = _rows2d(out)
-    assert x.dtype == torch.bfloat16 and w_il.dtype == torch.bfloat16 and w_il.is_contiguous() and tuple(w_il.shape) == (2 * F, K) and out.shape[0] == M
-    _check(lib().b200seq_linear_gated(_p(x), C.c_int64(ldx), _p(w_il), M, F, K, C.c_float(limit), C.c_float(alpha), C.c_float(up_shift), _p(out),
+    assert w_il.dtype == torch.bfloat16 and w_il.is_contiguous() and tuple(w_il.shape) == (2 * F, K) and out.shape[0] == M
+    _check(lib().b200seq_linear_gated(_p(x), _DT[x.dtype], C.c_int64(ldx), _p(w_il), M, F, K, C.c_float(limit), C.c_float(alpha), C.c_float(up_shift), _p(out),
                                       _DT[out.dtype], C.c_int64(ldo), _st(x)))
 
 

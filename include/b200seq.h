@@ -77,6 +77,11 @@ int b200seq_embed_streams(const void* table_bf16, const int32_t* ids, float scal
 int b200seq_hc_norm(float* X, const float* y, const float* post, const float* in_w, const float* norm_w, int S, int W, int groups, float eps,
                     const int32_t* rows, int R, void* out, int out_dtype, void* stream);
 
+/* The same followed by the sublayer's carried convolution (mode B200SEQ_CONV_RESIDUAL, no bias) in one kernel, for steps in which every
+ * entry brings exactly one token (st->T == st->B, all rows): out[t] = h + conv(h), conv_state[slot][taps-1][W] read and shifted. */
+int b200seq_hc_norm_conv(float* X, const float* y, const float* post, const float* in_w, const float* norm_w, int S, int W, int groups, float eps,
+                         const float* conv_w, float* conv_state, const b200seq_step* st, int taps, void* out, int out_dtype, void* stream);
+
 /* Per-channel causal convolution over time with the last taps-1 inputs of every sequence carried in
  * state[slot][taps-1][C] (f32; read as zero when ent_pos0 == 0, rewritten for every entry of the step).
  * x: f32 rows of stride ldx; w: f32 [C, taps] (last column = current token); bias f32 [C] or null. */
@@ -94,11 +99,12 @@ int b200seq_gated_act(const float* gu, int64_t ldg, int T, int F, float limit, f
 /* y[M, N] (f32, stride ldy) = x[M, K] (f32 or bf16, stride ldx) . w[N, K]^T (bf16, contiguous) */
 int b200seq_linear(const void* x, int x_dtype, int64_t ldx, const void* w_bf16, int M, int N, int K, float* y, int64_t ldy, int path, void* stream);
 
-/* Fused gate|up projection + gated activation on the tensor-core path: w_il is the stacked weight [2F, K] with rows alternating
- * (gate 0, up 0, gate 1, up 1, ...); out[M, F] (act dtype, stride ldo) = gated_act(x . w_il^T) with the formula of b200seq_gated_act.
- * The [M, 2F] product is never written.  Needs bf16 activations, K % 8 == 0 and 16-byte aligned rows (B200SEQ_ERR_UNSUPPORTED otherwise). */
-int b200seq_linear_gated(const void* x_bf16, int64_t ldx, const void* w_il_bf16, int M, int F, int K, float limit, float alpha, float up_shift, void* out,
-                         int out_dtype, int64_t ldo, void* stream);
+/* Fused gate|up projection + gated activation: w_il is the stacked weight [2F, K] with rows alternating (gate 0, up 0, gate 1, up 1, ...);
+ * out[M, F] (act dtype, stride ldo) = gated_act(x . w_il^T) with the formula of b200seq_gated_act.  The [M, 2F] product is never written.
+ * M <= 8: weight-streaming rows (f32 or bf16 activations); more rows: the tensor-core path, which needs bf16 activations, K % 8 == 0 and
+ * 16-byte aligned rows (B200SEQ_ERR_UNSUPPORTED otherwise). */
+int b200seq_linear_gated(const void* x, int x_dtype, int64_t ldx, const void* w_il_bf16, int M, int F, int K, float limit, float alpha, float up_shift,
+                         void* out, int out_dtype, int64_t ldo, void* stream);
 
 /* Attention over a paged f32 KV pool (kpool [blocks][block_size][G][D], vpool [..][G][V]).
  * qkvg: f32 [T, ld] = q (H*D) | k (G*D) | v (G*V) | gate (H, only if gated).

@@ -403,3 +403,45 @@ def test_attention_key_splits_agree_with_one_block(ops, H, G, D, V):
     for split in (True, False):
         got = run_attention(ops, {"a": q}, {"a": k}, {"a": v}, {"a": gate}, 0.3, 200, 0, 1e-6, plan, 16, 40, split=split)["a"]
         close(got, ref, 2e-5)
+
+
+@pytest.mark.parametrize("S,W,groups,taps", [(1, 40, 1, 1), (3, 48, 2, 3), (2, 33, 3, 4), (4, 1024, 2, 2)])
+def test_stream_mix_norm_and_convolution_in_one_kernel(ops, S, W, groups, taps):
+    """steps of one token per entry: stream update, collapse, norm and the carried convolution in one launch, against the separate
+    operators' restatement over whole sequences; a sequence's first token must not read what its slot held before"""
+    steps, eps = 9, 1e-4
+    seqs = {"a": 0, "b": 3, "c": 1}                       # name -> slot
+    X = {n: rnd(steps, S, W, seed=400 + i) for i, n in enumerate(seqs)}
+    y = {n: rnd(steps, W, seed=410 + i) for i, n in enumerate(seqs)}
+    outv, mix, inw, nw, cw = rnd(S, seed=420), rnd(S, S, seed=421), rnd(S, seed=422), rnd(W, seed=423), rnd(W, taps, seed=424)
+    ref = {}
+    for n in seqs:
+        Xn = torch.einsum("st,nsw->ntw", mix.double(), X[n].double()) + outv.double()[None, :, None] * y[n].double()[:, None, :]
+        h = O.group_rms(torch.einsum("s,nsw->nw", inw.double(), Xn), groups, eps, nw.double())
+        ref[n] = h + O.causal_conv(h, cw.double())
+    state = torch.full((4, max(taps - 1, 1), W), 77.0, device=DEV)
+    post = torch.cat([outv, mix.reshape(-1)]).to(DEV)
+    for t in range(steps):
+        names = [n for n in seqs if not (n == "c" and t < 4)]       # c joins late, in a's and b's company
+        pos = {n: t - (4 if n == "c" else 0) for n in names}
+        d, keep = dev_step(ops, [(1, pos[n], seqs[n], [0]) for n in names], 4096)
+        Xd = torch.stack([X[n][pos[n]] for n in names]).to(DEV).contiguous()
+        yd = torch.stack([y[n][pos[n]] for n in names]).to(DEV).contiguous()
+        out = torch.empty(len(names), W, device=DEV)
+        ops.hc_norm_conv(Xd, yd, post, inw.to(DEV), nw.to(DEV), groups, eps, cw.to(DEV), state, d, out)
+        for i, n in enumerate(names):
+            close(out[i], ref[n][pos[n]], 2e-5)
+
+
+@pytest.mark.parametrize("M,F,K", [(1, 37, 40), (4, 64, 96), (8, 130, 200)])
+@pytest.mark.parametrize("xdt", [torch.float32, torch.bfloat16])
+def test_gate_up_projection_with_few_rows(ops, M, F, K, xdt):
+    limit = 0.9
+    x, wg, wu = rnd(M, K, seed=500).to(xdt), rnd(F, K, seed=501, scale=K ** -0.5).bfloat16(), rnd(F, K, seed=502, scale=K ** -0.5).bfloat16()
+    g = torch.clamp(x.double() @ wg.double().T, max=limit)
+    u = torch.clamp(x.double() @ wu.double().T, -limit, limit)
+    ref = g * torch.sigmoid(1.702 * g) * (u + 1.0)
+    w_il = torch.stack([wg, wu], 1).reshape(2 * F, K).contiguous()
+    out = torch.empty(M, F, device=DEV)
+    ops.linear_gated(x.to(DEV), w_il.to(DEV), limit, 1.702, 1.0, out)
+    close(out, ref, 1e-5)

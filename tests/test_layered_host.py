@@ -202,3 +202,16 @@ def test_run_entries_admits_advances_and_releases():
     assert m.steps[1].ent_pos0.tolist() == [1] and "a" not in eng.cache.live and eng.cache.live["b"].n_tokens == 3
     with pytest.raises(ValueError):
         eng.run_entries([{"id": "b", "tokens": [1], "want": []}, {"id": "b", "tokens": [2], "want": []}], [])
+
+
+def test_sequence_library_exports_what_its_header_declares():
+    import re
+
+    from blazr_b200 import seqops
+    here = os.path.dirname(os.path.abspath(__file__))
+    txt = re.sub(r"/\*.*?\*/", "", open(os.path.join(here, "..", "include", "b200seq.h")).read(), flags=re.S)
+    syms = sorted(set(re.findall(r"\b(b200seq_[a-z0-9_]+)\s*\(", txt)))
+    L = seqops.lib()
+    for s in syms:
+        assert hasattr(L, s), f"{s} declared in b200seq.h but not exported"
+    assert sorted(seqops.EXPORTS) == syms
