@@ -198,7 +198,7 @@ class Decoder:
         # M <= 4: dp4a matvec on int8 activation records (bit-exact contract); M > 4 (batched decode, reference
         # src/engine/batch_decode.rs:115-147): tcgen05 dequant-GEMM on f32 activations (1e-2 tolerance contract)
         self.wide = batch > 4
-        assert not (self.wide and tp_world > 1), "batched decode is single-GPU in this round"
+        assert not (self.wide and tp_world > 1), "batched decode is single-GPU"
         if paged:
             max_ctx = -(-max_ctx // block_size) * block_size   # whole blocks
         self.c, self.cfg, self.scheme, self.M, self.max_ctx = client, cfg, scheme, batch, max_ctx

@@ -7,7 +7,7 @@ dense-attention decoder (blazr_b200/decode.py, Q8_0 weights) of the same width, 
                algorithmic bytes / FLOPs and the fraction of the roofline it reaches; the like kernels of the decoder beside them
 
 `python bench.py --layered fenorax [--layered-sizes w1024,w2048]` prints the result as one JSON line; bench.py's default workload
-and contract are untouched.
+and JSON line are untouched.
 """
 from __future__ import annotations
 
