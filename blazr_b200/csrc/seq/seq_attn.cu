@@ -65,7 +65,7 @@ struct AttnArgs {
     const float* qkvg;
     int64_t ld;
     const float *kpool, *vpool;
-    int H, G, D, V, Rb, HB, QT, nsplit;
+    int H, G, D, V, Rb, HB, QT, nsplit, share_kv;   // share_kv: V tiles reuse the K tile's shared memory (large heads: more blocks per SM)
     float scale;
     int chunk, window, gated;
     void* out;
@@ -96,15 +96,16 @@ __device__ __forceinline__ float dot4(const float4 a, const float4 b, float acc)
 }
 
 template <int RT, int VPT>
-__global__ void __launch_bounds__(AT_NT, (RT == 4 && VPT == 4) ? 3 : 1) attn_tile_kernel(const AttnArgs a, const b200seq_step st) {
+__global__ void __launch_bounds__(AT_NT, (VPT == 4) ? 3 : (VPT == 8 ? 2 : 1)) attn_tile_kernel(const AttnArgs a, const b200seq_step st) {
     extern __shared__ __align__(16) float sm[];
     constexpr int RQ = 16 * RT, VS = 16 * VPT, PS = AT_KT + 4;
     const int D = a.D, V = a.V, H = a.H, G = a.G;
     const int Dp = (D + 3) & ~3, QS = Dp + 4;
     float* Qs = sm;                     // [RQ][QS]
     float* Ks = Qs + RQ * QS;           // [AT_KT][QS]
-    float* Vs = Ks + AT_KT * QS;        // [AT_KT][VS]
-    float* Ps = Vs + AT_KT * VS;        // [RQ][PS]
+    const int kv_floats = a.share_kv ? max(AT_KT * QS, AT_KT * VS) : AT_KT * QS;
+    float* Vs = a.share_kv ? Ks : Ks + AT_KT * QS;   // [AT_KT][VS]
+    float* Ps = a.share_kv ? Ks + kv_floats : Vs + AT_KT * VS;   // [RQ][PS]
     const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
     int e, t0, nq;
     if (!attn_find_tile(st, blockIdx.x, a.QT, e, t0, nq)) return;
@@ -147,6 +148,23 @@ __global__ void __launch_bounds__(AT_NT, (RT == 4 && VPT == 4) ? 3 : 1) attn_til
         for (int j = 0; j < VPT; ++j) acc[i][j] = 0.f;
     }
     const bool vecD = (D & 3) == 0, vecV = (V & 3) == 0;
+    auto load_v = [&](int k0) {
+        if (vecV) {
+            for (int idx = tid; idx < AT_KT * (VS >> 2); idx += AT_NT) {
+                const int k = idx / (VS >> 2), c4 = idx - k * (VS >> 2);
+                const int kp = k0 + k;
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (kp <= hi && 4 * c4 < V) v = *reinterpret_cast<const float4*>(a.vpool + (((int64_t)bt[kp / bs] * bs + kp % bs) * G + g) * V + 4 * c4);
+                *reinterpret_cast<float4*>(Vs + k * VS + 4 * c4) = v;
+            }
+        } else {
+            for (int idx = tid; idx < AT_KT * VS; idx += AT_NT) {
+                const int k = idx / VS, c = idx - k * VS;
+                const int kp = k0 + k;
+                Vs[k * VS + c] = (kp <= hi && c < V) ? a.vpool[(((int64_t)bt[kp / bs] * bs + kp % bs) * G + g) * V + c] : 0.f;
+            }
+        }
+    };
     int tile = 0;
     for (int k0 = kbeg; k0 <= hi; k0 += AT_KT, ++tile) {
         if (tile % a.nsplit != split) continue;
@@ -167,21 +185,7 @@ __global__ void __launch_bounds__(AT_NT, (RT == 4 && VPT == 4) ? 3 : 1) attn_til
                 Ks[k * QS + d] = (kp <= hi && d < D) ? a.kpool[(((int64_t)bt[kp / bs] * bs + kp % bs) * G + g) * D + d] : 0.f;
             }
         }
-        if (vecV) {
-            for (int idx = tid; idx < AT_KT * (VS >> 2); idx += AT_NT) {
-                const int k = idx / (VS >> 2), c4 = idx - k * (VS >> 2);
-                const int kp = k0 + k;
-                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (kp <= hi && 4 * c4 < V) v = *reinterpret_cast<const float4*>(a.vpool + (((int64_t)bt[kp / bs] * bs + kp % bs) * G + g) * V + 4 * c4);
-                *reinterpret_cast<float4*>(Vs + k * VS + 4 * c4) = v;
-            }
-        } else {
-            for (int idx = tid; idx < AT_KT * VS; idx += AT_NT) {
-                const int k = idx / VS, c = idx - k * VS;
-                const int kp = k0 + k;
-                Vs[k * VS + c] = (kp <= hi && c < V) ? a.vpool[(((int64_t)bt[kp / bs] * bs + kp % bs) * G + g) * V + c] : 0.f;
-            }
-        }
+        if (!a.share_kv) load_v(k0);
         __syncthreads();
         float s[RT][4];
 #pragma unroll
@@ -233,6 +237,10 @@ __global__ void __launch_bounds__(AT_NT, (RT == 4 && VPT == 4) ? 3 : 1) attn_til
             for (int j = 0; j < 4; ++j) Ps[(ty * RT + i) * PS + tx + 16 * j] = s[i][j];
         }
         __syncthreads();
+        if (a.share_kv) {   // every thread is done with the K tile: the V tile takes its place
+            load_v(k0);
+            __syncthreads();
+        }
         for (int k = 0; k < AT_KT; k += 4) {
             float4 p[RT];
 #pragma unroll
@@ -361,10 +369,15 @@ int b200seq_attn(const float* qkvg, int64_t ld, const b200seq_step* st, const fl
     if (window > 0 && window < max_keys) max_keys = window;
     AttnPlan p = attn_plan(st->T, st->B, H, G, max_keys);
     if (p.nsplit > 1 && (!scratch || scratch_floats < (size_t)st->T * H * p.nsplit * (V + 2))) p.nsplit = 1;
-    AttnArgs a{qkvg, ld, kpool, vpool, H, G, D, V, p.Rb, p.HB, p.QT, p.nsplit, scale, chunk, window, gated, out, out_dtype, scratch, error_flag_dev()};
+    AttnArgs a{qkvg, ld, kpool, vpool, H, G, D, V, p.Rb, p.HB, p.QT, p.nsplit, 0, scale, chunk, window, gated, out, out_dtype, scratch, error_flag_dev()};
     const int VPT = V <= 64 ? 4 : (V <= 128 ? 8 : 16);
     const int RQ = 16 * p.RT, QS = ((D + 3) & ~3) + 4;
-    const size_t smem = ((size_t)(RQ + AT_KT) * QS + (size_t)AT_KT * 16 * VPT + (size_t)RQ * (AT_KT + 4)) * sizeof(float);
+    size_t smem = ((size_t)(RQ + AT_KT) * QS + (size_t)AT_KT * 16 * VPT + (size_t)RQ * (AT_KT + 4)) * sizeof(float);
+    if (smem > 72 * 1024) {   // fewer than three blocks per SM would fit: let V reuse the K tile
+        a.share_kv = 1;
+        const size_t kv = (size_t)AT_KT * (QS > 16 * VPT ? QS : 16 * VPT);
+        smem = ((size_t)RQ * QS + kv + (size_t)RQ * (AT_KT + 4)) * sizeof(float);
+    }
     if (smem > 220 * 1024) return fail(B200SEQ_ERR_UNSUPPORTED, "attn: head size too large");
     dim3 grid(p.tiles, G * p.HB, p.nsplit);
     cudaStream_t cs = (cudaStream_t)stream;
