@@ -148,6 +148,8 @@ class LayeredModel:
 
         self.embed = lin("embed")
         self.final_norm = vec("final.norm")
+        if tuple(self.embed.shape) != (cfg.vocab, W) or self.final_norm.numel() != W:
+            raise ValueError("embedding / final norm shapes do not fit the configuration")
         self.ones_in = torch.ones(S, dtype=torch.float32, device=dev)
         self.layers: List[Dict[str, object]] = []
         self.max_proj = self.max_xbc = self.max_inner = 1
@@ -162,6 +164,9 @@ class LayeredModel:
                 names = [p + "mix.q", p + "mix.k", p + "mix.v"] + ([p + "mix.g"] if m.gated else [])
                 L["w_in"] = lin(*names)
                 L["w_o"] = lin(p + "mix.o")
+                n_in = m.heads * m.dim + m.kv_heads * (m.dim + m.vdim) + (m.heads if m.gated else 0)
+                if tuple(L["w_in"].shape) != (n_in, W) or tuple(L["w_o"].shape) != (W, m.heads * m.vdim):
+                    raise ValueError(f"layer {i}: attention tensor shapes do not fit the configuration")
                 self.max_inner = max(self.max_inner, m.heads * m.vdim)
             elif ls.kind == "ssm":
                 L["w_in"] = lin(p + "mix.in")
@@ -183,6 +188,8 @@ class LayeredModel:
                 gu = lin(p + "mlp.gate", p + "mlp.up")          # stored with alternating rows (gate j, up j): the pair meets in one warp
                 L["w_gu"] = gu.view(2, ls.ff.ff, W).transpose(0, 1).reshape(2 * ls.ff.ff, W).contiguous()
                 L["w_down"] = lin(p + "mlp.down")
+                if tuple(gu.shape) != (2 * ls.ff.ff, W) or tuple(L["w_down"].shape) != (W, ls.ff.ff):
+                    raise ValueError(f"layer {i}: feed-forward tensor shapes do not fit the configuration")
                 self.max_proj = max(self.max_proj, 2 * ls.ff.ff)
                 self.max_inner = max(self.max_inner, ls.ff.ff)
                 self.weight_bytes += (L["w_gu"].numel() + L["w_down"].numel()) * 2
