@@ -109,7 +109,9 @@ __global__ void __launch_bounds__(128) linear_tc_kernel(const __grid_constant__ 
     __shared__ uint32_t tmem_base;
     __shared__ int abort_flag;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
+    // token tiles vary fastest: the CTAs that run together share a few weight tiles and all activation tiles, which L2 holds, so the
+    // weights cross HBM once instead of once per token tile
+    const int n0 = blockIdx.y * BN, m0 = blockIdx.x * BM;
     const int nk = (p.K + BK - 1) / BK;
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) mbar_init(&full[s], 1), mbar_init(&empty[s], 1);
@@ -232,7 +234,7 @@ int launch(const void* x, int64_t ldx, const void* w, TcParams p, cudaStream_t s
         attr_set = true;
     }
     p.err = error_flag_dev();
-    dim3 grid((p.N + BN - 1) / BN, (p.M + BM - 1) / BM);
+    dim3 grid((p.M + BM - 1) / BM, (p.N + BN - 1) / BN);
     linear_tc_kernel<<<grid, 128, smem, st>>>(mw, mx, p);
     SEQ_LAUNCH_CHECK("linear tc");
     return 0;
