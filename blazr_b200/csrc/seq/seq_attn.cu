@@ -149,40 +149,31 @@ __global__ void __launch_bounds__(AT_NT, (VPT == 4) ? 3 : (VPT == 8 ? 2 : 1)) at
     }
     const bool vecD = (D & 3) == 0, vecV = (V & 3) == 0;
     auto load_v = [&](int k0) {
+        const int k = tid >> 2, sub = tid & 3;
+        const int kp = k0 + k;
+        const bool in = kp <= hi;
+        const float* src = in ? a.vpool + (((int64_t)bt[kp / bs] * bs + kp % bs) * G + g) * V : nullptr;
         if (vecV) {
-            for (int idx = tid; idx < AT_KT * (VS >> 2); idx += AT_NT) {
-                const int k = idx / (VS >> 2), c4 = idx - k * (VS >> 2);
-                const int kp = k0 + k;
-                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (kp <= hi && 4 * c4 < V) v = *reinterpret_cast<const float4*>(a.vpool + (((int64_t)bt[kp / bs] * bs + kp % bs) * G + g) * V + 4 * c4);
-                *reinterpret_cast<float4*>(Vs + k * VS + 4 * c4) = v;
-            }
+            for (int c4 = sub; c4 < (VS >> 2); c4 += 4)
+                *reinterpret_cast<float4*>(Vs + k * VS + 4 * c4) = (in && 4 * c4 < V) ? *reinterpret_cast<const float4*>(src + 4 * c4) : make_float4(0.f, 0.f, 0.f, 0.f);
         } else {
-            for (int idx = tid; idx < AT_KT * VS; idx += AT_NT) {
-                const int k = idx / VS, c = idx - k * VS;
-                const int kp = k0 + k;
-                Vs[k * VS + c] = (kp <= hi && c < V) ? a.vpool[(((int64_t)bt[kp / bs] * bs + kp % bs) * G + g) * V + c] : 0.f;
-            }
+            for (int c = sub; c < VS; c += 4) Vs[k * VS + c] = (in && c < V) ? src[c] : 0.f;
         }
     };
     int tile = 0;
     for (int k0 = kbeg; k0 <= hi; k0 += AT_KT, ++tile) {
         if (tile % a.nsplit != split) continue;
         __syncthreads();   // the previous tile's products are done with Ks, Vs, Ps (and Qs is written before the first)
-        if (vecD) {
-            const int d4n = D >> 2;
-            for (int idx = tid; idx < AT_KT * d4n; idx += AT_NT) {
-                const int k = idx / d4n, d4 = idx - k * d4n;
-                const int kp = k0 + k;
-                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (kp <= hi) v = *reinterpret_cast<const float4*>(a.kpool + (((int64_t)bt[kp / bs] * bs + kp % bs) * G + g) * D + 4 * d4);
-                *reinterpret_cast<float4*>(Ks + k * QS + 4 * d4) = v;
-            }
-        } else {
-            for (int idx = tid; idx < AT_KT * Dp; idx += AT_NT) {
-                const int k = idx / Dp, d = idx - k * Dp;
-                const int kp = k0 + k;
-                Ks[k * QS + d] = (kp <= hi && d < D) ? a.kpool[(((int64_t)bt[kp / bs] * bs + kp % bs) * G + g) * D + d] : 0.f;
+        {   // four threads per key: the page lookup happens once per thread and tile
+            const int k = tid >> 2, sub = tid & 3;
+            const int kp = k0 + k;
+            const bool in = kp <= hi;
+            const float* src = in ? a.kpool + (((int64_t)bt[kp / bs] * bs + kp % bs) * G + g) * D : nullptr;
+            if (vecD) {
+                for (int d4 = sub; d4 < (D >> 2); d4 += 4)
+                    *reinterpret_cast<float4*>(Ks + k * QS + 4 * d4) = in ? *reinterpret_cast<const float4*>(src + 4 * d4) : make_float4(0.f, 0.f, 0.f, 0.f);
+            } else {
+                for (int d = sub; d < Dp; d += 4) Ks[k * QS + d] = (in && d < D) ? src[d] : 0.f;
             }
         }
         if (!a.share_kv) load_v(k0);

@@ -57,7 +57,8 @@ template <int NPL, int MODE>
 __global__ void __launch_bounds__(SSM_WARPS * 32) ssm_kernel(const SsmArgs a, const b200seq_step st) {
     extern __shared__ __align__(16) float sm[];
     const int H = a.H, V = a.V, N = a.N, NL = a.NL;
-    const int cpw = 32 / NL, cols = SSM_WARPS * cpw;       // value columns of this block
+    const int cpw = 32 / NL, cols = SSM_WARPS * cpw;       // value columns of this block (NL, cpw, cols and NPL are powers of two)
+    const int cols_shift = 31 - __clz(cols), npl_shift = 31 - __clz(NPL), nn_shift = npl_shift + (31 - __clz(NL));
     const int nstride = NPL + 4;                           // padded chunk of one sub-lane (conflict-free 16-byte reads)
     const int nrow = NL * nstride;
     float* Bs = sm;                          // [SSM_TT][nrow]
@@ -96,9 +97,9 @@ __global__ void __launch_bounds__(SSM_WARPS * 32) ssm_kernel(const SsmArgs a, co
     for (int i0 = 0; i0 < len; i0 += SSM_TT) {
         const int nt = min(SSM_TT, len - i0);
         __syncthreads();
-        for (int idx = tid; idx < nt * NL * NPL; idx += blockDim.x) {
-            const int tt = idx / (NL * NPL), n = idx - tt * (NL * NPL);
-            const int at = tt * nrow + (n / NPL) * nstride + n % NPL;
+        for (int idx = tid; idx < (nt << nn_shift); idx += blockDim.x) {
+            const int tt = idx >> nn_shift, n = idx & ((1 << nn_shift) - 1);
+            const int at = tt * nrow + (n >> npl_shift) * nstride + (n & (NPL - 1));
             float b = 0.f, c = 0.f;
             if (n < N) {
                 const float* r = a.xbc + (int64_t)(row0 + i0 + tt) * a.ldx + inner + (int64_t)g * N + n;
@@ -108,8 +109,8 @@ __global__ void __launch_bounds__(SSM_WARPS * 32) ssm_kernel(const SsmArgs a, co
             Bs[at] = b;
             Cs[at] = c;
         }
-        for (int idx = tid; idx < nt * cols; idx += blockDim.x) {
-            const int tt = idx / cols, c = idx - tt * cols;
+        for (int idx = tid; idx < (nt << cols_shift); idx += blockDim.x) {
+            const int tt = idx >> cols_shift, c = idx & (cols - 1);
             const int64_t row = row0 + i0 + tt;
             const bool in = v0 + c < V;
             xs[idx] = in ? a.xbc[row * a.ldx + (int64_t)h * V + v0 + c] : 0.f;
@@ -150,8 +151,8 @@ __global__ void __launch_bounds__(SSM_WARPS * 32) ssm_kernel(const SsmArgs a, co
         }
         if (MODE != SSM_LOCAL) {
             __syncthreads();
-            for (int idx = tid; idx < nt * cols; idx += blockDim.x) {
-                const int tt = idx / cols, c = idx - tt * cols;
+            for (int idx = tid; idx < (nt << cols_shift); idx += blockDim.x) {
+                const int tt = idx >> cols_shift, c = idx & (cols - 1);
                 if (v0 + c < V) a.out[(int64_t)(row0 + i0 + tt) * inner + (int64_t)h * V + v0 + c] = xs[idx];
             }
         }
