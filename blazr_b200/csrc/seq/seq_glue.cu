@@ -57,6 +57,7 @@ __global__ void hc_norm_kernel(float* __restrict__ X, const float* __restrict__ 
     extern __shared__ __align__(16) float sm[];
     float* u = sm;
     float* red = sm + W;
+    float* rs = red + 40;        // [groups]: 1 / rms of every group (convolution variant)
     const int r = blockIdx.x;
     const int64_t t = rows ? rows[r] : r;
     float mixr[S * S], outr[S], inr[S];
@@ -131,25 +132,58 @@ __global__ void hc_norm_kernel(float* __restrict__ X, const float* __restrict__ 
         const float rinv = 1.0f / sqrtf(ss / (float)Wg + eps);
         if (!cv.w) {
             for (int i = threadIdx.x; i < Wg; i += blockDim.x) store_act(out, out_dtype, (int64_t)r * W + g * Wg + i, u[g * Wg + i] * rinv * norm_w[g * Wg + i]);
-            continue;
+        } else if (threadIdx.x == 0) {
+            rs[g] = rinv;
         }
-        const int hist = cv.taps - 1;
-        const bool fresh = cv.ent_pos0[r] == 0;
-        float* sp = cv.state + (int64_t)cv.ent_slot[r] * hist * W;
-        for (int i = threadIdx.x; i < Wg; i += blockDim.x) {
-            const int c = g * Wg + i;
-            const float hv = u[c] * rinv * norm_w[c];
-            const float* wc = cv.w + (int64_t)c * cv.taps;
-            float acc = wc[hist] * hv;
-            float next = hv;                           // what row j receives: the old row j + 1 (the new h for the last row)
-            for (int j = hist - 1; j >= 0; --j) {
-                const float old = fresh ? 0.f : sp[(int64_t)j * W + c];
-                acc = fmaf(wc[j], old, acc);
-                sp[(int64_t)j * W + c] = next;
-                next = old;
+    }
+    if (!cv.w) return;
+    __syncthreads();
+    // convolution.  All old state rows and taps of a batch of the thread's channels are fetched before any of them is stored: the
+    // stores would otherwise order every later load behind them (one memory round trip per channel).
+    constexpr int HC_U = 8, HC_T = 4;
+    const int hist = cv.taps - 1;
+    const bool fresh = cv.ent_pos0[r] == 0;
+    float* sp = cv.state + (int64_t)cv.ent_slot[r] * hist * W;
+    if (cv.taps <= HC_T) {
+        for (int base = 0; base < W; base += HC_U * blockDim.x) {
+            float cold[HC_U][HC_T - 1], cw[HC_U][HC_T];
+#pragma unroll
+            for (int k = 0; k < HC_U; ++k) {
+                const int c = base + threadIdx.x + k * blockDim.x;
+#pragma unroll
+                for (int j = 0; j < HC_T; ++j) cw[k][j] = (c < W && j < cv.taps) ? cv.w[(int64_t)c * cv.taps + j] : 0.f;
+#pragma unroll
+                for (int j = 0; j < HC_T - 1; ++j) cold[k][j] = (c < W && j < hist && !fresh) ? sp[(int64_t)j * W + c] : 0.f;
             }
-            store_act(out, out_dtype, (int64_t)r * W + c, hv + acc);
+#pragma unroll
+            for (int k = 0; k < HC_U; ++k) {
+                const int c = base + threadIdx.x + k * blockDim.x;
+                if (c < W) {
+                    const float hv = u[c] * rs[c / Wg] * norm_w[c];
+                    float acc = 0.f;
+#pragma unroll
+                    for (int j = 0; j < HC_T; ++j) acc = fmaf(cw[k][j], j == hist ? hv : (j < hist ? cold[k][j < HC_T - 1 ? j : 0] : 0.f), acc);
+#pragma unroll
+                    for (int j = 0; j < HC_T - 1; ++j)       // row j receives the old row j + 1, the last row the new h
+                        if (j < hist) sp[(int64_t)j * W + c] = j == hist - 1 ? hv : cold[k][j + 1 < HC_T - 1 ? j + 1 : 0];
+                    store_act(out, out_dtype, (int64_t)r * W + c, hv + acc);
+                }
+            }
         }
+        return;
+    }
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        const float hv = u[c] * rs[c / Wg] * norm_w[c];
+        const float* wc = cv.w + (int64_t)c * cv.taps;
+        float acc = wc[hist] * hv;
+        float next = hv;                           // what row j receives: the old row j + 1 (the new h for the last row)
+        for (int j = hist - 1; j >= 0; --j) {
+            const float old = fresh ? 0.f : sp[(int64_t)j * W + c];
+            acc = fmaf(wc[j], old, acc);
+            sp[(int64_t)j * W + c] = next;
+            next = old;
+        }
+        store_act(out, out_dtype, (int64_t)r * W + c, hv + acc);
     }
 }
 
@@ -369,14 +403,23 @@ static int hc_norm_launch(float* X, const float* y, const float* post, const flo
     if (!X || S < 1 || S > MAX_STREAMS || W < 1 || R < 0) return fail(B200SEQ_ERR_INVALID_ARG, "hc_norm: bad arguments");
     if ((y && !post) || (norm_w && (!in_w || !out || groups < 1 || W % groups))) return fail(B200SEQ_ERR_INVALID_ARG, "hc_norm: missing parameters or width not divisible by groups");
     if (R == 0) return 0;
-    const size_t smem = ((size_t)W + 40) * sizeof(float);
+    const size_t smem = ((size_t)W + 40 + (cv.w ? groups : 0)) * sizeof(float);
     if (smem > 200 * 1024) return fail(B200SEQ_ERR_UNSUPPORTED, "hc_norm: width %d too large", W);
     const bool vec = W % 4 == 0 && (reinterpret_cast<uintptr_t>(X) & 15) == 0 && (!y || (reinterpret_cast<uintptr_t>(y) & 15) == 0);
-    const int nt = W >= 2048 ? 512 : (W >= 512 ? 256 : 128);
+    const int nt_want = W >= 2048 ? 512 : (W >= 512 ? 256 : 128);
     cudaError_t e = cudaSuccess;
 #define HC_LAUNCH(S_, VW_)                                                                                                                   \
     do {                                                                                                                                     \
-        if (smem > 48 * 1024) e = cudaFuncSetAttribute(hc_norm_kernel<S_, VW_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
+        static int max_threads = 0;   /* what the instantiation's register use allows */                                                    \
+        if (!max_threads) {                                                                                                                  \
+            cudaFuncAttributes fa;                                                                                                           \
+            e = cudaFuncGetAttributes(&fa, hc_norm_kernel<S_, VW_>);                                                                         \
+            if (e == cudaSuccess) max_threads = fa.maxThreadsPerBlock;                                                                       \
+        }                                                                                                                                    \
+        int nt = nt_want;                                                                                                                    \
+        while (e == cudaSuccess && nt > max_threads && nt > 32) nt >>= 1;                                                                    \
+        if (e == cudaSuccess && smem > 48 * 1024)                                                                                            \
+            e = cudaFuncSetAttribute(hc_norm_kernel<S_, VW_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                       \
         if (e == cudaSuccess)                                                                                                                \
             hc_norm_kernel<S_, VW_><<<R, nt, smem, (cudaStream_t)stream>>>(X, y, post, in_w, norm_w, W, groups, eps, rows, out, out_dtype, cv);  \
     } while (0)

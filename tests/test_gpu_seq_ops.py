@@ -104,7 +104,7 @@ def test_linear_row_does_not_depend_on_the_batch(ops):
         assert torch.equal(one[0], full[17])
 
 
-@pytest.mark.parametrize("S,W,groups", [(1, 40, 1), (3, 48, 2), (4, 30, 5), (8, 1200, 3)])
+@pytest.mark.parametrize("S,W,groups", [(1, 40, 1), (3, 48, 2), (4, 30, 5), (8, 1200, 3), (8, 4096, 4), (6, 2304, 2)])
 def test_stream_mix_and_group_norm(ops, S, W, groups):
     T, eps = 5, 1e-3
     X, y = rnd(T, S, W, seed=5), rnd(T, W, seed=6)
@@ -405,7 +405,7 @@ def test_attention_key_splits_agree_with_one_block(ops, H, G, D, V):
         close(got, ref, 2e-5)
 
 
-@pytest.mark.parametrize("S,W,groups,taps", [(1, 40, 1, 1), (3, 48, 2, 3), (2, 33, 3, 4), (4, 1024, 2, 2)])
+@pytest.mark.parametrize("S,W,groups,taps", [(1, 40, 1, 1), (3, 48, 2, 3), (2, 33, 3, 4), (4, 1024, 2, 2), (6, 4224, 2, 4), (2, 64, 1, 6), (8, 8200, 5, 3)])
 def test_stream_mix_norm_and_convolution_in_one_kernel(ops, S, W, groups, taps):
     """steps of one token per entry: stream update, collapse, norm and the carried convolution in one launch, against the separate
     operators' restatement over whole sequences; a sequence's first token must not read what its slot held before"""
