@@ -52,6 +52,7 @@ __global__ void __launch_bounds__(256) linear_rows_kernel(const XT* __restrict__
 #pragma unroll
         for (int m = 0; m < MB; ++m) acc0[m] = acc1[m] = 0.f;
         if (VEC) {
+#pragma unroll 4
             for (int k = lane * 8; k < K; k += 256) {
                 float a[8], b[8];
                 bf16x8_to_f32(__ldg(reinterpret_cast<const uint4*>(w0 + k)), a);
