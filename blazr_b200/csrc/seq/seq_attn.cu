@@ -1,7 +1,11 @@
 // seq_attn.cu -- attention of a flat mixed batch (prompt portions beside single decoded tokens) over a paged f32 KV pool.
-//   prep  : per-head unit-RMS q and k (no weight), k and v rows stored at the token's page slot.
+//   prep  : per-head unit-RMS q and k (no weight) and / or rotary positions (interleaved pairs, per-pair frequencies from a table, so
+//           that any frequency scaling is the caller's), k and v rows stored at the token's page slot; the values may be the keys
+//           as projected.  With pooling, a second kernel writes the mean key and mean value of every block of positions the step
+//           completes (from the pool's rows, in position order: the result does not depend on how the prompt was cut).
 //   attend: tiles of (token, query head) rows against tiles of the keys they can see (the token's own chunk and / or window, read
-//           through the entry's block table); scores, soft-max and the weighted sum in f32; optional per-head sigmoid gate.
+//           through the entry's block table, and with pooling the pooled entries of the blocks that lie wholly before the window,
+//           in the same soft-max); scores, soft-max and the weighted sum in f32; optional per-head sigmoid gate.
 // A row's result depends on the token's position and on its sequence's pages only; the rest of the batch changes at most how the
 // keys are split among blocks (rounding).
 #include "seq_common.cuh"
@@ -17,36 +21,87 @@ __device__ __forceinline__ int64_t kv_row(const b200seq_step& st, int e, int pos
     return (int64_t)st.block_table[(int64_t)e * st.max_blocks + b] * st.block_size + pos % st.block_size;
 }
 
+// pooled entry of block b (positions b * P .. b * P + P - 1) of a sequence: it lives in the page of the block's first position, at
+// the block's rank among the blocks that start in that page
+__device__ __forceinline__ int64_t pooled_row(const int32_t* bt, int bs, int P, int ppp, int b) {
+    const int pg = (b * P) / bs;
+    const int first = (pg * bs + P - 1) / P;
+    return (int64_t)bt[pg] * ppp + (b - first);
+}
+
 // grid (T), one warp per head unit: H query heads, G key heads, G value heads
-__global__ void attn_prep_kernel(float* __restrict__ qkvg, int64_t ld, b200seq_step st, float* __restrict__ kpool, float* __restrict__ vpool, int H, int G,
-                                 int D, int V, float qk_eps, int* err) {
+__global__ void attn_prep_kernel(float* __restrict__ proj, int64_t ld, b200seq_step st, const b200seq_attn_desc a, float* __restrict__ kpool,
+                                 float* __restrict__ vpool, int* err) {
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
     const int e = st.tok_ent[t];
-    const int64_t row = kv_row(st, e, st.tok_pos[t], err);
-    float* base = qkvg + (int64_t)t * ld;
+    const int pos = st.tok_pos[t];
+    const int64_t row = kv_row(st, e, pos, err);
+    float* base = proj + (int64_t)t * ld;
+    const int H = a.H, G = a.G, D = a.D, V = a.V;
     for (int u = wid; u < H + 2 * G; u += nw) {
-        if (u < H + G) {   // q or k head: normalise
-            float* p = base + (int64_t)u * D;   // q heads then k heads are contiguous
+        if (u < H + G) {   // q or k head: normalise, rotate
+            float* p = u < H ? base + a.q_col + (int64_t)u * D : base + a.k_col + (int64_t)(u - H) * D;
             float rinv = 1.f;
-            if (qk_eps >= 0.f) {
+            if (a.qk_eps >= 0.f) {
                 float ss = 0.f;
                 for (int d = lane; d < D; d += 32) ss = fmaf(p[d], p[d], ss);
                 ss = warp_sum(ss);
-                rinv = 1.0f / sqrtf(ss / (float)D + qk_eps);
+                rinv = 1.0f / sqrtf(ss / (float)D + a.qk_eps);
             }
-            if (u < H) {
-                for (int d = lane; d < D; d += 32) p[d] *= rinv;
-            } else if (row >= 0) {
-                float* dst = kpool + (row * G + (u - H)) * D;
-                for (int d = lane; d < D; d += 32) dst[d] = p[d] * rinv;
+            float* dst = u < H ? p : (row >= 0 ? kpool + (row * G + (u - H)) * D : nullptr);
+            for (int d0 = 0; d0 < D; d0 += 32) {   // a pair (2i, 2i + 1) lies in one pass: both are read before either is written
+                const int d = d0 + lane;
+                float v = 0.f;
+                if (d < D) {
+                    v = p[d] * rinv;
+                    if (d < a.rot_dims) {
+                        const float other = p[d ^ 1] * rinv;
+                        float sn, cs;
+                        sincosf((float)pos * a.rot_freq[d >> 1], &sn, &cs);
+                        sn *= a.rot_scale, cs *= a.rot_scale;
+                        v = (d & 1) ? fmaf(v, cs, other * sn) : fmaf(v, cs, -other * sn);
+                    }
+                }
+                __syncwarp();
+                if (d < D && dst) dst[d] = v;
             }
         } else if (row >= 0) {
             const int g = u - H - G;
-            const float* p = base + (int64_t)(H + G) * D + (int64_t)g * V;
+            const float* p = base + a.v_col + (int64_t)g * V;
             float* dst = vpool + (row * G + g) * V;
             for (int d = lane; d < V; d += 32) dst[d] = p[d];
         }
+    }
+}
+
+// grid (T): the token that completes a block of P positions writes the block's mean key and mean value
+__global__ void attn_pool_kernel(b200seq_step st, int G, int D, int V, int P, int ppp, const float* __restrict__ kpool, const float* __restrict__ vpool,
+                                 float* __restrict__ kpp, float* __restrict__ vpp, int* err) {
+    const int t = blockIdx.x;
+    const int pos = st.tok_pos[t];
+    if ((pos + 1) % P != 0) return;
+    const int e = st.tok_ent[t];
+    const int bs = st.block_size;
+    if (pos / bs >= st.max_blocks || pos < 0) {
+        if (threadIdx.x == 0) atomicOr(err, 1);
+        return;
+    }
+    const int32_t* bt = st.block_table + (int64_t)e * st.max_blocks;
+    const int b = pos / P;
+    const int64_t prow = pooled_row(bt, bs, P, ppp, b);
+    const int nk = G * D, nv = G * V;
+    const float inv = 1.0f / (float)P;
+    for (int c = threadIdx.x; c < nk + nv; c += blockDim.x) {
+        const bool isk = c < nk;
+        const float* src = isk ? kpool : vpool;
+        const int cc = isk ? c : c - nk, wdt = isk ? nk : nv;
+        float acc = 0.f;
+        for (int j = 0; j < P; ++j) {
+            const int pj = b * P + j;
+            acc += src[((int64_t)bt[pj / bs] * bs + pj % bs) * wdt + cc];
+        }
+        (isk ? kpp : vpp)[prow * wdt + cc] = acc * inv;
     }
 }
 
@@ -65,6 +120,9 @@ struct AttnArgs {
     const float* qkvg;
     int64_t ld;
     const float *kpool, *vpool;
+    const float *kpp, *vpp;   // pooled keys / values, pool > 0
+    int pool, ppp;            // positions per pooled block; pooled entries per page
+    int q_col, gate_col;
     int H, G, D, V, Rb, HB, QT, nsplit, share_kv;   // share_kv: V tiles reuse the K tile's shared memory (large heads: more blocks per SM)
     float scale;
     int chunk, window, gated;
@@ -126,10 +184,10 @@ __global__ void __launch_bounds__(AT_NT, (VPT == 4) ? 3 : (VPT == 8 ? 2 : 1)) at
     for (int idx = tid; idx < RQ * Dp; idx += AT_NT) {
         const int r = idx / Dp, d = idx - r * Dp;
         const int tq = r / a.Rb, hr = r - tq * a.Rb;
-        Qs[r * QS + d] = (tq < nq && hr < nh && d < D) ? a.qkvg[(int64_t)(t0 + tq) * a.ld + (int64_t)(h0 + hr) * D + d] : 0.f;
+        Qs[r * QS + d] = (tq < nq && hr < nh && d < D) ? a.qkvg[(int64_t)(t0 + tq) * a.ld + a.q_col + (int64_t)(h0 + hr) * D + d] : 0.f;
     }
     // per-row limits of the visible keys
-    int rlo[RT], rhi[RT];
+    int rlo[RT], rhi[RT], rnb[RT];   // visible positions [rlo, rhi]; visible pooled blocks [0, rnb)
     float m[RT], l[RT], acc[RT][VPT];
 #pragma unroll
     for (int i = 0; i < RT; ++i) {
@@ -140,19 +198,26 @@ __global__ void __launch_bounds__(AT_NT, (VPT == 4) ? 3 : (VPT == 8 ? 2 : 1)) at
             int lo = a.chunk > 0 ? (p / a.chunk) * a.chunk : 0;
             if (a.window > 0) lo = max(lo, p - a.window + 1);
             rlo[i] = lo, rhi[i] = p;
+            rnb[i] = (a.pool > 0 && p - a.window + 1 > 0) ? (p - a.window + 1) / a.pool : 0;
         } else {
-            rlo[i] = 1, rhi[i] = 0;   // sees nothing
+            rlo[i] = 1, rhi[i] = 0, rnb[i] = 0;   // sees nothing
         }
         m[i] = -INFINITY, l[i] = 0.f;
 #pragma unroll
         for (int j = 0; j < VPT; ++j) acc[i][j] = 0.f;
     }
     const bool vecD = (D & 3) == 0, vecV = (V & 3) == 0;
-    auto load_v = [&](int k0) {
+    // pooled blocks every row of the tile may see (the tile's last row sees the most), then the positions from kbeg to hi
+    const int nbmax = (a.pool > 0 && hi - a.window + 1 > 0) ? (hi - a.window + 1) / a.pool : 0;
+    const int npt = (nbmax + AT_KT - 1) / AT_KT;
+    const int ntiles = npt + (hi - kbeg) / AT_KT + 1;
+    auto load_v = [&](int k0, bool pooled) {
         const int k = tid >> 2, sub = tid & 3;
         const int kp = k0 + k;
-        const bool in = kp <= hi;
-        const float* src = in ? a.vpool + (((int64_t)bt[kp / bs] * bs + kp % bs) * G + g) * V : nullptr;
+        const bool in = pooled ? kp < nbmax : kp <= hi;
+        const float* src = !in ? nullptr
+                           : pooled ? a.vpp + (pooled_row(bt, bs, a.pool, a.ppp, kp) * G + g) * V
+                                    : a.vpool + (((int64_t)bt[kp / bs] * bs + kp % bs) * G + g) * V;
         if (vecV) {
             for (int c4 = sub; c4 < (VS >> 2); c4 += 4)
                 *reinterpret_cast<float4*>(Vs + k * VS + 4 * c4) = (in && 4 * c4 < V) ? *reinterpret_cast<const float4*>(src + 4 * c4) : make_float4(0.f, 0.f, 0.f, 0.f);
@@ -160,15 +225,18 @@ __global__ void __launch_bounds__(AT_NT, (VPT == 4) ? 3 : (VPT == 8 ? 2 : 1)) at
             for (int c = sub; c < VS; c += 4) Vs[k * VS + c] = (in && c < V) ? src[c] : 0.f;
         }
     };
-    int tile = 0;
-    for (int k0 = kbeg; k0 <= hi; k0 += AT_KT, ++tile) {
+    for (int tile = 0; tile < ntiles; ++tile) {
         if (tile % a.nsplit != split) continue;
+        const bool pooled = tile < npt;
+        const int k0 = pooled ? tile * AT_KT : kbeg + (tile - npt) * AT_KT;
         __syncthreads();   // the previous tile's products are done with Ks, Vs, Ps (and Qs is written before the first)
         {   // four threads per key: the page lookup happens once per thread and tile
             const int k = tid >> 2, sub = tid & 3;
             const int kp = k0 + k;
-            const bool in = kp <= hi;
-            const float* src = in ? a.kpool + (((int64_t)bt[kp / bs] * bs + kp % bs) * G + g) * D : nullptr;
+            const bool in = pooled ? kp < nbmax : kp <= hi;
+            const float* src = !in ? nullptr
+                               : pooled ? a.kpp + (pooled_row(bt, bs, a.pool, a.ppp, kp) * G + g) * D
+                                        : a.kpool + (((int64_t)bt[kp / bs] * bs + kp % bs) * G + g) * D;
             if (vecD) {
                 for (int d4 = sub; d4 < (D >> 2); d4 += 4)
                     *reinterpret_cast<float4*>(Ks + k * QS + 4 * d4) = in ? *reinterpret_cast<const float4*>(src + 4 * d4) : make_float4(0.f, 0.f, 0.f, 0.f);
@@ -176,7 +244,7 @@ __global__ void __launch_bounds__(AT_NT, (VPT == 4) ? 3 : (VPT == 8 ? 2 : 1)) at
                 for (int d = sub; d < Dp; d += 4) Ks[k * QS + d] = (in && d < D) ? src[d] : 0.f;
             }
         }
-        if (!a.share_kv) load_v(k0);
+        if (!a.share_kv) load_v(k0, pooled);
         __syncthreads();
         float s[RT][4];
 #pragma unroll
@@ -200,7 +268,8 @@ __global__ void __launch_bounds__(AT_NT, (VPT == 4) ? 3 : (VPT == 8 ? 2 : 1)) at
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const int kp = k0 + tx + 16 * j;
-                s[i][j] = (kp >= rlo[i] && kp <= rhi[i]) ? s[i][j] * a.scale : -INFINITY;
+                const bool seen = pooled ? kp < rnb[i] : (kp >= rlo[i] && kp <= rhi[i]);
+                s[i][j] = seen ? s[i][j] * a.scale : -INFINITY;
                 mx = fmaxf(mx, s[i][j]);
             }
 #pragma unroll
@@ -229,7 +298,7 @@ __global__ void __launch_bounds__(AT_NT, (VPT == 4) ? 3 : (VPT == 8 ? 2 : 1)) at
         }
         __syncthreads();
         if (a.share_kv) {   // every thread is done with the K tile: the V tile takes its place
-            load_v(k0);
+            load_v(k0, pooled);
             __syncthreads();
         }
         for (int k = 0; k < AT_KT; k += 4) {
@@ -261,7 +330,7 @@ __global__ void __launch_bounds__(AT_NT, (VPT == 4) ? 3 : (VPT == 8 ? 2 : 1)) at
         const int t = t0 + tq, h = h0 + hr;
         if (a.nsplit == 1) {
             float gate = 1.f;
-            if (a.gated) gate = sigmoidf_acc(a.qkvg[(int64_t)t * a.ld + (int64_t)(H + G) * D + (int64_t)G * V + h]);
+            if (a.gated) gate = sigmoidf_acc(a.qkvg[(int64_t)t * a.ld + a.gate_col + h]);
             const float f = gate / l[i];
 #pragma unroll
             for (int jv = 0; jv < VPT / 4; ++jv)
@@ -297,7 +366,7 @@ __global__ void attn_merge_kernel(const AttnArgs a) {
         if (ms != -INFINITY) L = fmaf(pp[s * (V + 2) + 1], expf(ms - M), L);
     }
     float gate = 1.f;
-    if (a.gated) gate = sigmoidf_acc(a.qkvg[(int64_t)t * a.ld + (int64_t)(a.H + a.G) * a.D + (int64_t)a.G * V + h]);
+    if (a.gated) gate = sigmoidf_acc(a.qkvg[(int64_t)t * a.ld + a.gate_col + h]);
     for (int c = threadIdx.x; c < V; c += blockDim.x) {
         float o = 0.f;
         for (int s = 0; s < ns; ++s) {
@@ -334,33 +403,67 @@ static AttnPlan attn_plan(int T, int B, int H, int G, int max_keys) {
 
 using namespace b200seq;
 
-extern "C" {
-
-int b200seq_attn_prep(float* qkvg, int64_t ld, const b200seq_step* st, float* kpool, float* vpool, int H, int G, int D, int V, float qk_eps, void* stream) {
-    if (!qkvg || !st || !kpool || !vpool || H < 1 || G < 1 || H % G || D < 1 || V < 1) return fail(B200SEQ_ERR_INVALID_ARG, "attn_prep: bad arguments");
-    if (st->T == 0) return 0;
-    attn_prep_kernel<<<st->T, 256, 0, (cudaStream_t)stream>>>(qkvg, ld, *st, kpool, vpool, H, G, D, V, qk_eps, error_flag_dev());
-    SEQ_LAUNCH_CHECK("attn_prep");
+static int desc_check(const b200seq_attn_desc* d, const char* what) {
+    if (!d || d->H < 1 || d->G < 1 || d->H % d->G || d->D < 1 || d->V < 1 || d->q_col < 0 || d->k_col < 0 || d->v_col < 0)
+        return fail(B200SEQ_ERR_INVALID_ARG, "%s: bad head counts, sizes or columns", what);
+    if (d->v_col == d->k_col && d->V != d->D) return fail(B200SEQ_ERR_INVALID_ARG, "%s: values taken from the keys need V == D", what);
+    if (d->rot_dims < 0 || d->rot_dims > d->D || (d->rot_dims & 1) || (d->rot_dims > 0 && !d->rot_freq))
+        return fail(B200SEQ_ERR_INVALID_ARG, "%s: rotary dimensions must be even, at most D, with a frequency table", what);
+    if (d->pool < 0 || (d->pool > 0 && d->window < 1)) return fail(B200SEQ_ERR_INVALID_ARG, "%s: pooled blocks need a window", what);
     return 0;
 }
 
+extern "C" {
+
+int b200seq_attn_prep_ex(float* proj, int64_t ld, const b200seq_step* st, const b200seq_attn_desc* d, float* kpool, float* vpool, float* kpooled, float* vpooled,
+                         void* stream) {
+    if (!proj || !st || !kpool || !vpool) return fail(B200SEQ_ERR_INVALID_ARG, "attn_prep: bad arguments");
+    if (int rc = desc_check(d, "attn_prep")) return rc;
+    if (d->pool > 0 && (!kpooled || !vpooled)) return fail(B200SEQ_ERR_INVALID_ARG, "attn_prep: pooled blocks need their pools");
+    if (st->T == 0) return 0;
+    attn_prep_kernel<<<st->T, 256, 0, (cudaStream_t)stream>>>(proj, ld, *st, *d, kpool, vpool, error_flag_dev());
+    SEQ_LAUNCH_CHECK("attn_prep");
+    if (d->pool > 0) {
+        const int ppp = (st->block_size + d->pool - 1) / d->pool;
+        attn_pool_kernel<<<st->T, 128, 0, (cudaStream_t)stream>>>(*st, d->G, d->D, d->V, d->pool, ppp, kpool, vpool, kpooled, vpooled, error_flag_dev());
+        SEQ_LAUNCH_CHECK("attn_pool");
+    }
+    return 0;
+}
+
+int b200seq_attn_prep(float* qkvg, int64_t ld, const b200seq_step* st, float* kpool, float* vpool, int H, int G, int D, int V, float qk_eps, void* stream) {
+    const b200seq_attn_desc d{H, G, D, V, 0, H * D, (H + G) * D, -1, 1.f, 0, 0, 0, qk_eps, 0, nullptr, 1.f};
+    return b200seq_attn_prep_ex(qkvg, ld, st, &d, kpool, vpool, nullptr, nullptr, stream);
+}
+
+static int attn_max_keys(const b200seq_step* st, int chunk, int window, int pool) {
+    const int ctx = st->max_blocks * st->block_size;
+    int max_keys = ctx;
+    if (chunk > 0 && chunk < max_keys) max_keys = chunk;
+    if (window > 0 && window < max_keys) max_keys = window;
+    if (pool > 0) max_keys += ctx / pool;
+    return max_keys;
+}
 size_t b200seq_attn_scratch_floats(int T, int B, int H, int G, int V, int max_keys) {
     if (T < 1 || B < 1 || H < 1 || G < 1 || H % G) return 0;
     const AttnPlan p = attn_plan(T, B, H, G, max_keys);
     return p.nsplit > 1 ? (size_t)T * H * p.nsplit * (V + 2) : 0;
 }
 
-int b200seq_attn(const float* qkvg, int64_t ld, const b200seq_step* st, const float* kpool, const float* vpool, int H, int G, int D, int V, float scale,
-                 int chunk, int window, int gated, void* out, int out_dtype, float* scratch, size_t scratch_floats, void* stream) {
-    if (!qkvg || !st || !kpool || !vpool || !out || H < 1 || G < 1 || H % G || D < 1 || V < 1 || V > 256)
-        return fail(B200SEQ_ERR_INVALID_ARG, "attn: bad arguments (value size <= 256)");
+int b200seq_attn_ex(const float* qkvg, int64_t ld, const b200seq_step* st, const b200seq_attn_desc* d, const float* kpool, const float* vpool,
+                    const float* kpooled, const float* vpooled, void* out, int out_dtype, float* scratch, size_t scratch_floats, void* stream) {
+    if (!qkvg || !st || !kpool || !vpool || !out) return fail(B200SEQ_ERR_INVALID_ARG, "attn: bad arguments");
+    if (int rc = desc_check(d, "attn")) return rc;
+    if (d->V > 256) return fail(B200SEQ_ERR_INVALID_ARG, "attn: value size <= 256");
+    if (d->pool > 0 && (!kpooled || !vpooled)) return fail(B200SEQ_ERR_INVALID_ARG, "attn: pooled blocks need their pools");
     if (st->T == 0) return 0;
-    int max_keys = st->max_blocks * st->block_size;
-    if (chunk > 0 && chunk < max_keys) max_keys = chunk;
-    if (window > 0 && window < max_keys) max_keys = window;
+    const int H = d->H, G = d->G, D = d->D, V = d->V, gated = d->gate_col >= 0;
+    const int max_keys = attn_max_keys(st, d->chunk, d->window, d->pool);
     AttnPlan p = attn_plan(st->T, st->B, H, G, max_keys);
     if (p.nsplit > 1 && (!scratch || scratch_floats < (size_t)st->T * H * p.nsplit * (V + 2))) p.nsplit = 1;
-    AttnArgs a{qkvg, ld, kpool, vpool, H, G, D, V, p.Rb, p.HB, p.QT, p.nsplit, 0, scale, chunk, window, gated, out, out_dtype, scratch, error_flag_dev()};
+    const int ppp = d->pool > 0 ? (st->block_size + d->pool - 1) / d->pool : 0;
+    AttnArgs a{qkvg, ld, kpool, vpool, kpooled, vpooled, d->pool, ppp, d->q_col, d->gate_col, H, G, D, V, p.Rb, p.HB, p.QT, p.nsplit, 0, d->scale, d->chunk, d->window,
+               gated, out, out_dtype, scratch, error_flag_dev()};
     const int VPT = V <= 64 ? 4 : (V <= 128 ? 8 : 16);
     const int RQ = 16 * p.RT, QS = ((D + 3) & ~3) + 4;
     size_t smem = ((size_t)(RQ + AT_KT) * QS + (size_t)AT_KT * 16 * VPT + (size_t)RQ * (AT_KT + 4)) * sizeof(float);
@@ -399,6 +502,12 @@ int b200seq_attn(const float* qkvg, int64_t ld, const b200seq_step* st, const fl
         SEQ_LAUNCH_CHECK("attn merge");
     }
     return 0;
+}
+
+int b200seq_attn(const float* qkvg, int64_t ld, const b200seq_step* st, const float* kpool, const float* vpool, int H, int G, int D, int V, float scale,
+                 int chunk, int window, int gated, void* out, int out_dtype, float* scratch, size_t scratch_floats, void* stream) {
+    const b200seq_attn_desc d{H, G, D, V, 0, H * D, (H + G) * D, gated ? (H + G) * D + G * V : -1, scale, chunk, window, 0, -1.f, 0, nullptr, 1.f};
+    return b200seq_attn_ex(qkvg, ld, st, &d, kpool, vpool, nullptr, nullptr, out, out_dtype, scratch, scratch_floats, stream);
 }
 
 }  // extern "C"

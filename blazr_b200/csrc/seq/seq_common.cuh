@@ -56,4 +56,28 @@ __device__ __forceinline__ float sigmoidf_acc(float x) { return 1.0f / (1.0f + e
 __device__ __forceinline__ float siluf_acc(float x) { return x / (1.0f + expf(-x)); }
 __device__ __forceinline__ float softplusf_acc(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 
+
+// activation of a projection (include/b200seq.h: B200SEQ_ACT_*)
+struct ActParams {
+    int kind;
+    float limit, alpha, shift;
+};
+__device__ __forceinline__ bool act_is_gated(int kind) { return kind == B200SEQ_ACT_SWISH_CLAMP || kind == B200SEQ_ACT_GELU_TANH; }
+__device__ __forceinline__ float gelu_tanhf_acc(float z) { return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z))); }
+__device__ __forceinline__ float act_gated(const ActParams& a, float gate, float up) {
+    if (a.kind == B200SEQ_ACT_GELU_TANH) return gelu_tanhf_acc(gate) * up;
+    const float g = fminf(gate, a.limit);
+    const float u = fminf(fmaxf(up, -a.limit), a.limit);
+    return g * sigmoidf_acc(a.alpha * g) * (u + a.shift);
+}
+__device__ __forceinline__ float act_plain(int kind, float z) {
+    if (kind == B200SEQ_ACT_RELU2) {
+        const float r = fmaxf(z, 0.f);
+        return r * r;
+    }
+    return z;
+}
+inline bool act_kind_gated(int kind) { return kind == B200SEQ_ACT_SWISH_CLAMP || kind == B200SEQ_ACT_GELU_TANH; }
+inline bool act_kind_known(int kind) { return kind >= B200SEQ_ACT_SWISH_CLAMP && kind <= B200SEQ_ACT_RELU2; }
+
 }  // namespace b200seq

@@ -310,15 +310,18 @@ __global__ void group_rmsnorm_kernel(const float* __restrict__ x, int64_t ldx, c
     }
 }
 
-__global__ void gated_act_kernel(const float* __restrict__ gu, int64_t ldg, int T, int F, float limit, float alpha, float up_shift, int interleaved,
-                                 void* __restrict__ out, int out_dtype) {
+// F outputs per row; gated kinds read the pair (gate f, up f) from columns (2f, 2f + 1) (interleaved) or (f, F + f)
+__global__ void gated_act_kernel(const float* __restrict__ gu, int64_t ldg, int T, int F, const ActParams act, int interleaved, void* __restrict__ out,
+                                 int out_dtype, int64_t ldo) {
     const int64_t n = (int64_t)T * F;
+    const bool gated = act_is_gated(act.kind);
     for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (int64_t)gridDim.x * blockDim.x) {
         const int64_t t = idx / F;
         const int f = (int)(idx - t * F);
-        const float g = fminf(gu[t * ldg + (interleaved ? 2 * f : f)], limit);
-        const float u = fminf(fmaxf(gu[t * ldg + (interleaved ? 2 * f + 1 : F + f)], -limit), limit);
-        store_act(out, out_dtype, idx, g * sigmoidf_acc(alpha * g) * (u + up_shift));
+        float v;
+        if (gated) v = act_gated(act, gu[t * ldg + (interleaved ? 2 * f : f)], gu[t * ldg + (interleaved ? 2 * f + 1 : F + f)]);
+        else v = act_plain(act.kind, gu[t * ldg + f]);
+        store_act(out, out_dtype, t * ldo + f, v);
     }
 }
 
@@ -476,8 +479,19 @@ int b200seq_gated_act(const float* gu, int64_t ldg, int T, int F, float limit, f
     if (T == 0) return 0;
     const int64_t n = (int64_t)T * F;
     const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
-    gated_act_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(gu, ldg, T, F, limit, alpha, up_shift, interleaved, out, out_dtype);
+    gated_act_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(gu, ldg, T, F, ActParams{B200SEQ_ACT_SWISH_CLAMP, limit, alpha, up_shift}, interleaved, out, out_dtype, F);
     SEQ_LAUNCH_CHECK("gated_act");
+    return 0;
+}
+
+int b200seq_act(const float* z, int64_t ldz, int T, int N, int act, float limit, float alpha, float shift, void* out, int out_dtype, int64_t ldo, void* stream) {
+    if (!z || !out || T < 0 || N < 1 || !act_kind_known(act) || (act_kind_gated(act) && (N & 1))) return fail(B200SEQ_ERR_INVALID_ARG, "act: bad arguments");
+    if (T == 0) return 0;
+    const int F = act_kind_gated(act) ? N / 2 : N;
+    const int64_t n = (int64_t)T * F;
+    const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+    gated_act_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(z, ldz, T, F, ActParams{act, limit, alpha, shift}, 1, out, out_dtype, ldo);
+    SEQ_LAUNCH_CHECK("act");
     return 0;
 }
 

@@ -9,8 +9,8 @@ namespace b200seq {
 
 int launch_linear_tc(const void* x_bf16, int64_t ldx, const void* w_bf16, int M, int N, int K, float* y, int64_t ldy, cudaStream_t st);
 bool linear_tc_usable(int x_dtype, int64_t ldx, int M, int N, int K, const void* x, const void* w);
-int launch_linear_tc_gated(const void* x, int64_t ldx, const void* w_interleaved, int M, int F, int K, float limit, float alpha, float shift, void* out,
-                           int out_dtype, int64_t ldo, cudaStream_t st);
+int launch_linear_tc_act(const void* x, int64_t ldx, const void* w, int M, int N, int K, const ActParams act, void* out, int out_dtype, int64_t ldo,
+                         cudaStream_t st);
 
 template <typename XT>
 __device__ __forceinline__ float ld_x(const XT* p);
@@ -29,12 +29,13 @@ __device__ __forceinline__ void bf16x8_to_f32(const uint4 v, float* f) {
 }
 
 // MB tokens x 2 weight rows per warp.  VEC: K % 8 == 0 and 16-byte aligned rows (x rows too).
-// gated epilogue of a stacked gate|up weight with alternating rows: a warp's two rows are (gate j, up j); act[m][j] is written instead of y
+// activation epilogue: act[m][.] is written instead of y.  Gated kinds: the weight is a stacked gate|up with alternating rows, a warp's two
+// rows are (gate j, up j) and give output j; plain kinds: every row gives its own output.
 struct GateEpi {
     void* out;       // null: plain product to y
     int out_dtype;
     int64_t ldo;
-    float limit, alpha, shift;
+    ActParams act;
 };
 
 template <typename XT, int MB, bool VEC>
@@ -94,9 +95,12 @@ __global__ void __launch_bounds__(256) linear_rows_kernel(const XT* __restrict__
             const float s0 = warp_sum(acc0[m]), s1 = warp_sum(acc1[m]);
             if (lane == 0 && m0 + m < M) {
                 if (ge.out) {
-                    const float g = fminf(s0, ge.limit);
-                    const float u = fminf(fmaxf(s1, -ge.limit), ge.limit);
-                    store_act(ge.out, ge.out_dtype, (int64_t)(m0 + m) * ge.ldo + (n0 >> 1), g * sigmoidf_acc(ge.alpha * g) * (u + ge.shift));
+                    if (act_is_gated(ge.act.kind)) {
+                        store_act(ge.out, ge.out_dtype, (int64_t)(m0 + m) * ge.ldo + (n0 >> 1), act_gated(ge.act, s0, s1));
+                    } else {
+                        store_act(ge.out, ge.out_dtype, (int64_t)(m0 + m) * ge.ldo + n0, act_plain(ge.act.kind, s0));
+                        if (two) store_act(ge.out, ge.out_dtype, (int64_t)(m0 + m) * ge.ldo + n0 + 1, act_plain(ge.act.kind, s1));
+                    }
                 } else {
                     y[(int64_t)(m0 + m) * ldy + n0] = s0;
                     if (two) y[(int64_t)(m0 + m) * ldy + n0 + 1] = s1;
@@ -157,10 +161,10 @@ __global__ void __launch_bounds__(256) linear_tiled_kernel(const XT* __restrict_
 
 template <typename XT>
 static void launch_rows(const XT* x, int64_t ldx, const __nv_bfloat16* w, int M, int N, int K, float* y, int64_t ldy, cudaStream_t st,
-                        const GateEpi ge = GateEpi{nullptr, 0, 0, 0.f, 0.f, 0.f}) {
+                        const GateEpi ge = GateEpi{nullptr, 0, 0, ActParams{0, 0.f, 0.f, 0.f}}) {
     const bool vec = K % 8 == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
                      (ldx * (int64_t)sizeof(XT)) % 16 == 0;
-    const int rpw = (ge.out || (N + 15) / 16 >= 4 * 148) ? 2 : 1;   // few rows: one per warp, so that every SM streams weights
+    const int rpw = ((ge.out && act_kind_gated(ge.act.kind)) || (N + 15) / 16 >= 4 * 148) ? 2 : 1;   // few rows: one per warp, so that every SM streams weights
     const int warps = (N + rpw - 1) / rpw;
     const int blocks = (warps + 7) / 8;
     if (M <= 1) {
@@ -207,19 +211,27 @@ extern "C" int b200seq_linear(const void* x, int x_dtype, int64_t ldx, const voi
     return 0;
 }
 
-extern "C" int b200seq_linear_gated(const void* x, int x_dtype, int64_t ldx, const void* w, int M, int F, int K, float limit, float alpha, float up_shift,
-                                    void* out, int out_dtype, int64_t ldo, void* stream) {
-    if (!x || !w || !out || M < 0 || F < 1 || K < 1 || ldx < K || ldo < F) return fail(B200SEQ_ERR_INVALID_ARG, "linear_gated: bad arguments");
-    if (out_dtype != B200SEQ_F32 && out_dtype != B200SEQ_BF16) return fail(B200SEQ_ERR_INVALID_ARG, "linear_gated: output dtype");
-    if (x_dtype != B200SEQ_F32 && x_dtype != B200SEQ_BF16) return fail(B200SEQ_ERR_INVALID_ARG, "linear_gated: activation dtype");
+extern "C" int b200seq_linear_act(const void* x, int x_dtype, int64_t ldx, const void* w, int M, int N, int K, int act, float limit, float alpha, float shift,
+                                  void* out, int out_dtype, int64_t ldo, void* stream) {
+    if (!x || !w || !out || M < 0 || N < 1 || K < 1 || ldx < K || !act_kind_known(act)) return fail(B200SEQ_ERR_INVALID_ARG, "linear_act: bad arguments");
+    const bool gated = act_kind_gated(act);
+    if ((gated && (N & 1)) || ldo < (gated ? N / 2 : N)) return fail(B200SEQ_ERR_INVALID_ARG, "linear_act: output shape");
+    if (out_dtype != B200SEQ_F32 && out_dtype != B200SEQ_BF16) return fail(B200SEQ_ERR_INVALID_ARG, "linear_act: output dtype");
+    if (x_dtype != B200SEQ_F32 && x_dtype != B200SEQ_BF16) return fail(B200SEQ_ERR_INVALID_ARG, "linear_act: activation dtype");
     if (M == 0) return 0;
-    if (M <= 8) {   // few tokens: the weight-streaming kernel, a warp's two rows are one (gate, up) pair
-        const GateEpi ge{out, out_dtype, ldo, limit, alpha, up_shift};
-        if (x_dtype == B200SEQ_F32) launch_rows((const float*)x, ldx, (const __nv_bfloat16*)w, M, 2 * F, K, nullptr, 0, (cudaStream_t)stream, ge);
-        else launch_rows((const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w, M, 2 * F, K, nullptr, 0, (cudaStream_t)stream, ge);
-        SEQ_LAUNCH_CHECK("linear_gated rows");
+    const ActParams ap{act, limit, alpha, shift};
+    if (M <= 8) {   // few tokens: the weight-streaming kernel (gated kinds: a warp's two rows are one (gate, up) pair)
+        const GateEpi ge{out, out_dtype, ldo, ap};
+        if (x_dtype == B200SEQ_F32) launch_rows((const float*)x, ldx, (const __nv_bfloat16*)w, M, N, K, nullptr, 0, (cudaStream_t)stream, ge);
+        else launch_rows((const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w, M, N, K, nullptr, 0, (cudaStream_t)stream, ge);
+        SEQ_LAUNCH_CHECK("linear_act rows");
         return 0;
     }
-    if (!linear_tc_usable(x_dtype, ldx, M, 2 * F, K, x, w)) return fail(B200SEQ_ERR_UNSUPPORTED, "linear_gated: more than 8 rows need bf16 activations, K %% 8 == 0 and 16-byte aligned rows");
-    return launch_linear_tc_gated(x, ldx, w, M, F, K, limit, alpha, up_shift, out, out_dtype, ldo, (cudaStream_t)stream);
+    if (!linear_tc_usable(x_dtype, ldx, M, N, K, x, w)) return fail(B200SEQ_ERR_UNSUPPORTED, "linear_act: more than 8 rows need bf16 activations, K %% 8 == 0 and 16-byte aligned rows");
+    return launch_linear_tc_act(x, ldx, w, M, N, K, ap, out, out_dtype, ldo, (cudaStream_t)stream);
+}
+
+extern "C" int b200seq_linear_gated(const void* x, int x_dtype, int64_t ldx, const void* w, int M, int F, int K, float limit, float alpha, float up_shift,
+                                    void* out, int out_dtype, int64_t ldo, void* stream) {
+    return b200seq_linear_act(x, x_dtype, ldx, w, M, 2 * F, K, B200SEQ_ACT_SWISH_CLAMP, limit, alpha, up_shift, out, out_dtype, ldo, stream);
 }

@@ -10,8 +10,8 @@
 // runs under the other's main loop.  The k order of every output element is fixed (ascending slabs), whatever M is.
 //
 // Optional epilogue EPI_GATED for a stacked gate|up weight whose rows alternate (gate j, up j): neighbouring lanes hold the pair,
-// out[m][j] = g * sigmoid(alpha * g) * (u + shift) with g = min(gate, limit), u = clamp(up, +-limit) is written in the activation
-// type and the [M, 2F] product never reaches memory.
+// out[m][j] = act(gate, up) (clamped swish or tanh-gelu gate, seq_common.cuh) is written in the activation type and the [M, 2F]
+// product never reaches memory.  EPI_PLAIN_ACT applies an activation of one argument (squared relu) to every output.
 //
 // Every wait is bounded: a wait that runs out sets bit 1 of the library's error flags and the CTA leaves through the common
 // exit (its copies in flight are waited for, again bounded, and its tensor memory is freed).
@@ -97,10 +97,10 @@ struct TcParams {
     void* act_out;
     int64_t ldy, ldo;
     int M, N, K, epi, out_dtype;
-    float limit, alpha, shift;
+    ActParams act;
     int* err;
 };
-constexpr int EPI_NONE = 0, EPI_GATED = 1;
+constexpr int EPI_NONE = 0, EPI_GATED = 1, EPI_PLAIN_ACT = 2;
 
 __global__ void __launch_bounds__(128) linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const TcParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -178,16 +178,19 @@ __global__ void __launch_bounds__(128) linear_tc_kernel(const __grid_constant__ 
                     for (int j = 0; j < 16; ++j)
                         if (m0 + c + j < p.M) p.y[(int64_t)(m0 + c + j) * p.ldy + n] = __uint_as_float(r[j]);
                 }
+            } else if (p.epi == EPI_PLAIN_ACT) {
+                if (n < p.N) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        if (m0 + c + j < p.M) store_act(p.act_out, p.out_dtype, (int64_t)(m0 + c + j) * p.ldo + n, act_plain(p.act.kind, __uint_as_float(r[j])));
+                }
             } else {
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
                     const float mine = __uint_as_float(r[j]);
                     const float other = __shfl_xor_sync(0xffffffffu, mine, 1);
-                    if ((lane & 1) == 0 && n + 1 < p.N && m0 + c + j < p.M) {
-                        const float g = fminf(mine, p.limit);
-                        const float u = fminf(fmaxf(other, -p.limit), p.limit);
-                        store_act(p.act_out, p.out_dtype, (int64_t)(m0 + c + j) * p.ldo + (n >> 1), g * sigmoidf_acc(p.alpha * g) * (u + p.shift));
-                    }
+                    if ((lane & 1) == 0 && n + 1 < p.N && m0 + c + j < p.M)
+                        store_act(p.act_out, p.out_dtype, (int64_t)(m0 + c + j) * p.ldo + (n >> 1), act_gated(p.act, mine, other));
                 }
             }
         }
@@ -254,11 +257,11 @@ int launch_linear_tc(const void* x, int64_t ldx, const void* w, int M, int N, in
     return launch(x, ldx, w, p, st);
 }
 
-int launch_linear_tc_gated(const void* x, int64_t ldx, const void* w_interleaved, int M, int F, int K, float limit, float alpha, float shift, void* out,
-                           int out_dtype, int64_t ldo, cudaStream_t st) {
+int launch_linear_tc_act(const void* x, int64_t ldx, const void* w, int M, int N, int K, const ActParams act, void* out, int out_dtype, int64_t ldo,
+                         cudaStream_t st) {
     TcParams p{};
-    p.act_out = out, p.ldo = ldo, p.out_dtype = out_dtype, p.M = M, p.N = 2 * F, p.K = K, p.epi = EPI_GATED, p.limit = limit, p.alpha = alpha, p.shift = shift;
-    return launch(x, ldx, w_interleaved, p, st);
+    p.act_out = out, p.ldo = ldo, p.out_dtype = out_dtype, p.M = M, p.N = N, p.K = K, p.epi = act_kind_gated(act.kind) ? EPI_GATED : EPI_PLAIN_ACT, p.act = act;
+    return launch(x, ldx, w, p, st);
 }
 
 }  // namespace b200seq

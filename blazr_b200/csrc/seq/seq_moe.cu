@@ -1,0 +1,356 @@
+// seq_moe.cu -- mixture-of-experts feed-forward of layer-list models (bfloat16 expert weights [E][N][K], f32 accumulation).
+//   route   : sigmoid scores, group-limited choice of the `top` experts per token, weights normalised over the chosen ones (all f32).
+//   sort    : (token, choice) pairs ordered by expert, stable, so that one expert's rows form tiles.
+//   linear  : one projection of every pair through its expert's weight.  Few pairs (decode): one launch row per pair, the expert's
+//             weight rows streamed by warps with 16-byte loads.  Many pairs: 64 x 64 f32 fma tiles over each expert's sorted rows
+//             (exact 32-bit arithmetic; rows are gathered through the sort on load).
+//   combine : weighted sum of a token's expert outputs in choice order, plus an optional shared branch times a sigmoid token gate.
+// A pair's result depends on its token and expert only; which other tokens are in the step changes at most the kernel variant.
+#include "seq_common.cuh"
+
+namespace b200seq {
+
+constexpr int MOE_MAX_E = 1024;
+
+// grid (T), one warp per token
+__global__ void moe_route_kernel(const float* __restrict__ z, int64_t ldz, int E, int groups, int keep, int top, int32_t* __restrict__ ids,
+                                 float* __restrict__ wts, int32_t* __restrict__ counts) {
+    extern __shared__ float sm[];
+    float* s = sm;            // [E] scores; a chosen or excluded expert is marked by a negative value in `avail`
+    float* avail = sm + E;    // [E]
+    float* gsc = avail + E;   // [groups]
+    const int t = blockIdx.x, lane = threadIdx.x;
+    const float* zr = z + (int64_t)t * ldz;
+    for (int e = lane; e < E; e += 32) {
+        const float v = sigmoidf_acc(zr[e]);
+        s[e] = v, avail[e] = v;
+    }
+    __syncwarp();
+    if (groups > 1 && keep < groups) {
+        const int gs = E / groups;
+        for (int g = lane; g < groups; g += 32) {
+            float a = -1.f, b = -1.f;   // two largest
+            for (int i = 0; i < gs; ++i) {
+                const float v = s[g * gs + i];
+                if (v > a) b = a, a = v;
+                else if (v > b) b = v;
+            }
+            gsc[g] = gs > 1 ? a + b : a;
+        }
+        __syncwarp();
+        // the `keep` best groups stay: mark them by a negative score, then exclude the experts of every other group
+        for (int k = 0; k < keep; ++k) {
+            float best = -1.f;
+            int arg = 0x7fffffff;
+            for (int g = lane; g < groups; g += 32)
+                if (gsc[g] > best) best = gsc[g], arg = g;
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, arg, o);
+                if (ov > best || (ov == best && oi < arg)) best = ov, arg = oi;
+            }
+            if (lane == 0 && arg != 0x7fffffff) gsc[arg] = -2.f;
+            __syncwarp();
+        }
+        for (int e = lane; e < E; e += 32)
+            if (gsc[e / gs] != -2.f) avail[e] = -1.f;
+        __syncwarp();
+    }
+    float sum = 0.f;
+    for (int k = 0; k < top; ++k) {
+        float best = -1.f;
+        int arg = 0x7fffffff;
+        for (int e = lane; e < E; e += 32)
+            if (avail[e] > best) best = avail[e], arg = e;
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, arg, o);
+            if (ov > best || (ov == best && oi < arg)) best = ov, arg = oi;
+        }
+        if (arg == 0x7fffffff) arg = 0, best = 0.f;   // fewer allowed experts than `top`: cannot happen with a valid configuration
+        if (lane == 0) {
+            ids[(int64_t)t * top + k] = arg;
+            wts[(int64_t)t * top + k] = best;
+            avail[arg] = -1.f;
+            if (counts) atomicAdd(&counts[arg], 1);
+        }
+        sum += best;
+        __syncwarp();
+    }
+    const float inv = 1.0f / (sum + 1e-20f);
+    __syncwarp();
+    for (int k = lane; k < top; k += 32) wts[(int64_t)t * top + k] *= inv;
+}
+
+// grid (E), 256 threads: block e places the pairs of expert e behind those of the experts before it, in pair order
+__global__ void moe_sort_kernel(const int32_t* __restrict__ ids, int pairs, int E, const int32_t* __restrict__ counts, int32_t* __restrict__ offs,
+                                int32_t* __restrict__ sorted, int32_t* __restrict__ slot_of) {
+    __shared__ int seg[9];
+    __shared__ int red[8];
+    const int e = blockIdx.x, lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    int before = 0;
+    for (int i = threadIdx.x; i < e; i += blockDim.x) before += counts[i];
+    for (int o = 16; o > 0; o >>= 1) before += __shfl_xor_sync(0xffffffffu, before, o);
+    if (lane == 0) red[wid] = before;
+    __syncthreads();
+    int off = 0;
+    for (int w = 0; w < 8; ++w) off += red[w];
+    if (threadIdx.x == 0) {
+        offs[e] = off;
+        if (e == E - 1) offs[E] = off + counts[e];
+    }
+    const int per = ((pairs + 7) / 8 + 31) & ~31;   // a warp's contiguous share of the pairs
+    const int lo = wid * per, hi = min(pairs, lo + per);
+    int n = 0;
+    for (int p0 = lo; p0 < hi; p0 += 32) {
+        const int p = p0 + lane;
+        n += __popc(__ballot_sync(0xffffffffu, p < hi && ids[p] == e));
+    }
+    if (lane == 0) seg[wid + 1] = n;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        seg[0] = 0;
+        for (int w = 1; w <= 8; ++w) seg[w] += seg[w - 1];
+    }
+    __syncthreads();
+    int at = off + seg[wid];
+    for (int p0 = lo; p0 < hi; p0 += 32) {
+        const int p = p0 + lane;
+        const bool mine = p < hi && ids[p] == e;
+        const uint32_t bal = __ballot_sync(0xffffffffu, mine);
+        if (mine) {
+            const int slot = at + __popc(bal & ((1u << lane) - 1));
+            sorted[slot] = p;
+            slot_of[p] = slot;
+        }
+        at += __popc(bal);
+    }
+}
+
+__device__ __forceinline__ void bf16x8_f32(const uint4 v, float* f) {
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        f[2 * i] = __uint_as_float(u[i] << 16);
+        f[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u);
+    }
+}
+template <typename XT>
+__device__ __forceinline__ float ldx(const XT* p);
+template <>
+__device__ __forceinline__ float ldx<float>(const float* p) { return __ldg(p); }
+template <>
+__device__ __forceinline__ float ldx<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+
+struct MoeLin {
+    const void* x;
+    int64_t ldx;
+    int x_div;
+    const __nv_bfloat16* w;
+    const int32_t *ids, *sorted, *offs;
+    int pairs, E, N, K, act;
+    void* out;
+    int out_dtype;
+    int64_t ldo;
+};
+
+// grid (blocks of 8 warps over N, pairs): a warp = one output of one pair
+template <typename XT, bool VEC>
+__global__ void __launch_bounds__(256) moe_rows_kernel(const MoeLin a) {
+    const int lane = threadIdx.x & 31;
+    const int n = blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int p = blockIdx.y;
+    if (n >= a.N) return;
+    const int e = a.ids[p];
+    const __nv_bfloat16* wr = a.w + ((int64_t)e * a.N + n) * a.K;
+    const XT* xr = reinterpret_cast<const XT*>(a.x) + (int64_t)(a.x_div > 0 ? p / a.x_div : p) * a.ldx;
+    float acc = 0.f;
+    if (VEC) {
+#pragma unroll 4
+        for (int k = lane * 8; k < a.K; k += 256) {
+            float wv[8], xv[8];
+            bf16x8_f32(__ldg(reinterpret_cast<const uint4*>(wr + k)), wv);
+            if (sizeof(XT) == 4) {
+                const float4 q0 = __ldg(reinterpret_cast<const float4*>(xr + k)), q1 = __ldg(reinterpret_cast<const float4*>(xr + k) + 1);
+                xv[0] = q0.x, xv[1] = q0.y, xv[2] = q0.z, xv[3] = q0.w, xv[4] = q1.x, xv[5] = q1.y, xv[6] = q1.z, xv[7] = q1.w;
+            } else {
+                bf16x8_f32(__ldg(reinterpret_cast<const uint4*>(xr + k)), xv);
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc = fmaf(wv[i], xv[i], acc);
+        }
+    } else {
+        for (int k = lane; k < a.K; k += 32) acc = fmaf(__bfloat162float(wr[k]), ldx<XT>(xr + k), acc);
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) {
+        if (a.act < 0) reinterpret_cast<float*>(a.out)[(int64_t)p * a.ldo + n] = acc;
+        else store_act(a.out, a.out_dtype, (int64_t)p * a.ldo + n, act_plain(a.act, acc));
+    }
+}
+
+// 64 x 64 tiles over the sorted rows of one expert; grid (N tiles, upper bound of the row tiles of all experts)
+constexpr int MT = 64, MTK = 16;
+template <typename XT>
+__global__ void __launch_bounds__(256) moe_tiled_kernel(const MoeLin a) {
+    __shared__ float xs[MTK][MT + 4];
+    __shared__ float ws[MTK][MT + 4];
+    __shared__ int rowsrc[MT];
+    int e = 0, r0 = 0, rend = 0;
+    {   // which expert and which of its row tiles this block has
+        int acc = 0, idx = blockIdx.y;
+        bool found = false;
+        for (e = 0; e < a.E; ++e) {
+            const int b = a.offs[e], c = a.offs[e + 1] - b;
+            const int nt = (c + MT - 1) / MT;
+            if (idx < acc + nt) {
+                r0 = b + (idx - acc) * MT, rend = b + c;
+                found = true;
+                break;
+            }
+            acc += nt;
+        }
+        if (!found) return;
+    }
+    const int n0 = blockIdx.x * MT;
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    if (threadIdx.x < MT) {
+        const int r = r0 + threadIdx.x;
+        rowsrc[threadIdx.x] = r < rend ? (a.x_div > 0 ? a.sorted[r] / a.x_div : r) : -1;
+    }
+    __syncthreads();
+    const XT* x = reinterpret_cast<const XT*>(a.x);
+    const __nv_bfloat16* w = a.w + (int64_t)e * a.N * a.K;
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+    for (int k0 = 0; k0 < a.K; k0 += MTK) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int idx = threadIdx.x + i * 256;
+            const int r = idx >> 4, kk = idx & 15;
+            const int k = k0 + kk;
+            const int src = rowsrc[r];
+            xs[kk][r] = (src >= 0 && k < a.K) ? ldx<XT>(x + (int64_t)src * a.ldx + k) : 0.f;
+            ws[kk][r] = (n0 + r < a.N && k < a.K) ? __bfloat162float(w[(int64_t)(n0 + r) * a.K + k]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < MTK; ++kk) {
+            float av[4], bv[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) av[i] = xs[kk][ty * 4 + i], bv[i] = ws[kk][tx * 4 + i];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int r = r0 + ty * 4 + i;
+        if (r >= rend) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx * 4 + j;
+            if (n >= a.N) continue;
+            if (a.act < 0) reinterpret_cast<float*>(a.out)[(int64_t)r * a.ldo + n] = acc[i][j];
+            else store_act(a.out, a.out_dtype, (int64_t)r * a.ldo + n, act_plain(a.act, acc[i][j]));
+        }
+    }
+}
+
+// grid (T)
+__global__ void moe_combine_kernel(const float* __restrict__ ys, const float* __restrict__ wts, const int32_t* __restrict__ slot_of, int top, int W,
+                                   const float* __restrict__ shared, const float* __restrict__ gate_z, int64_t ldg, float* __restrict__ y) {
+    const int64_t t = blockIdx.x;
+    float gate = 1.f;
+    if (shared && gate_z) gate = sigmoidf_acc(gate_z[t * ldg]);
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        float acc = 0.f;
+        for (int j = 0; j < top; ++j) {
+            const int64_t p = t * top + j;
+            const int64_t slot = slot_of ? slot_of[p] : p;
+            acc = fmaf(wts[p], ys[slot * W + c], acc);
+        }
+        if (shared) acc = fmaf(gate, shared[t * W + c], acc);
+        y[t * W + c] = acc;
+    }
+}
+
+}  // namespace b200seq
+
+using namespace b200seq;
+
+extern "C" {
+
+int b200seq_moe_route(const float* z, int64_t ldz, int T, int E, int groups, int keep, int top, int32_t* ids, float* wts, int32_t* counts, void* stream) {
+    if (!z || !ids || !wts || T < 0 || E < 1 || E > MOE_MAX_E || top < 1 || top > E || ldz < E) return fail(B200SEQ_ERR_INVALID_ARG, "moe_route: bad arguments (experts <= %d)", MOE_MAX_E);
+    if (groups > 1 && (E % groups || keep < 1 || keep > groups || (int64_t)keep * (E / groups) < top))
+        return fail(B200SEQ_ERR_INVALID_ARG, "moe_route: groups must divide the experts and the kept groups must hold `top` experts");
+    cudaStream_t cs = (cudaStream_t)stream;
+    if (counts) {
+        cudaError_t e = cudaMemsetAsync(counts, 0, (size_t)E * sizeof(int32_t), cs);
+        if (e != cudaSuccess) return cuda_status(e, "moe_route memset");
+    }
+    if (T == 0) return 0;
+    const int g = groups > 1 ? groups : 1;
+    moe_route_kernel<<<T, 32, (size_t)(2 * E + g) * sizeof(float), cs>>>(z, ldz, E, g, groups > 1 ? keep : 1, top, ids, wts, counts);
+    SEQ_LAUNCH_CHECK("moe_route");
+    return 0;
+}
+
+int b200seq_moe_sort(const int32_t* ids, int pairs, int E, const int32_t* counts, int32_t* offs, int32_t* sorted, int32_t* slot_of, void* stream) {
+    if (!ids || !counts || !offs || !sorted || !slot_of || pairs < 0 || E < 1) return fail(B200SEQ_ERR_INVALID_ARG, "moe_sort: bad arguments");
+    moe_sort_kernel<<<E, 256, 0, (cudaStream_t)stream>>>(ids, pairs, E, counts, offs, sorted, slot_of);
+    SEQ_LAUNCH_CHECK("moe_sort");
+    return 0;
+}
+
+int b200seq_moe_linear(const void* x, int x_dtype, int64_t ldx_, int x_div, const void* w, const int32_t* ids, const int32_t* sorted, const int32_t* offs, int pairs,
+                       int E, int N, int K, int act, void* out, int out_dtype, int64_t ldo, void* stream) {
+    if (!x || !w || !out || pairs < 0 || E < 1 || N < 1 || K < 1 || ldx_ < K || ldo < N || x_div < 0) return fail(B200SEQ_ERR_INVALID_ARG, "moe_linear: bad arguments");
+    if (x_dtype != B200SEQ_F32 && x_dtype != B200SEQ_BF16) return fail(B200SEQ_ERR_INVALID_ARG, "moe_linear: activation dtype");
+    if (act >= 0 && (!act_kind_known(act) || act_kind_gated(act))) return fail(B200SEQ_ERR_INVALID_ARG, "moe_linear: only plain activation kinds");
+    if (act >= 0 && out_dtype != B200SEQ_F32 && out_dtype != B200SEQ_BF16) return fail(B200SEQ_ERR_INVALID_ARG, "moe_linear: output dtype");
+    if ((sorted == nullptr) != (offs == nullptr) || (!sorted && !ids)) return fail(B200SEQ_ERR_INVALID_ARG, "moe_linear: ids, or sorted with offs");
+    if (pairs == 0) return 0;
+    const MoeLin a{x, ldx_, x_div, (const __nv_bfloat16*)w, ids, sorted, offs, pairs, E, N, K, act, out, out_dtype, ldo};
+    cudaStream_t cs = (cudaStream_t)stream;
+    if (!sorted) {
+        const size_t es = x_dtype == B200SEQ_F32 ? 4 : 2;
+        const bool vec = K % 8 == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (ldx_ * es) % 16 == 0;
+        if (pairs > 65535) return fail(B200SEQ_ERR_UNSUPPORTED, "moe_linear: too many pairs for the row form");
+        dim3 grid((N + 7) / 8, pairs);
+        if (x_dtype == B200SEQ_F32) {
+            if (vec) moe_rows_kernel<float, true><<<grid, 256, 0, cs>>>(a);
+            else moe_rows_kernel<float, false><<<grid, 256, 0, cs>>>(a);
+        } else {
+            if (vec) moe_rows_kernel<__nv_bfloat16, true><<<grid, 256, 0, cs>>>(a);
+            else moe_rows_kernel<__nv_bfloat16, false><<<grid, 256, 0, cs>>>(a);
+        }
+        SEQ_LAUNCH_CHECK("moe_linear rows");
+        return 0;
+    }
+    const int tiles = (pairs + MT - 1) / MT + E;
+    if (tiles > 65535) return fail(B200SEQ_ERR_UNSUPPORTED, "moe_linear: too many row tiles");
+    dim3 grid((N + MT - 1) / MT, tiles);
+    if (x_dtype == B200SEQ_F32) moe_tiled_kernel<float><<<grid, 256, 0, cs>>>(a);
+    else moe_tiled_kernel<__nv_bfloat16><<<grid, 256, 0, cs>>>(a);
+    SEQ_LAUNCH_CHECK("moe_linear tiles");
+    return 0;
+}
+
+int b200seq_moe_combine(const float* ys, const float* wts, const int32_t* slot_of, int T, int top, int W, const float* shared, const float* gate_z, int64_t ldg,
+                        float* y, void* stream) {
+    if (!ys || !wts || !y || T < 0 || top < 1 || W < 1) return fail(B200SEQ_ERR_INVALID_ARG, "moe_combine: bad arguments");
+    if (T == 0) return 0;
+    moe_combine_kernel<<<T, W >= 1024 ? 256 : 128, 0, (cudaStream_t)stream>>>(ys, wts, slot_of, top, W, shared, gate_z, ldg, y);
+    SEQ_LAUNCH_CHECK("moe_combine");
+    return 0;
+}
+
+}  // extern "C"

@@ -1,8 +1,13 @@
 """Layer-list models: a model is a list of layers, each one token mixer (attention over the paged KV pool, or a state-space
-recurrence with per-slot state) plus an optional feed-forward, wrapped in the pieces a design switches on: several residual
-streams with learned mixing, grouped RMS norms, a short carried-state convolution in front of every sublayer.  The mechanisms
-are parameterised (window / chunk size, score scale, unit-norm epsilon, gate, state size, clamp limit, ...) so that another
-design can list them in another combination; blazr_b200/fenorax.py maps one design's config.json onto these specs.
+recurrence with per-slot state) plus an optional feed-forward (dense or a mixture of experts), wrapped in the pieces a design
+switches on.  Two layouts of the residual path exist:
+  "streams": sublayers in sequence over several residual streams with learned mixing, grouped RMS norms and a short
+             carried-state convolution in front of every sublayer (blazr_b200/fenorax.py);
+  "depth":   parallel layers (mixer and feed-forward read the same input through two layer norms), one residual stream whose
+             layer inputs are learned averages over the results of all earlier layers (blazr_b200/gemosun.py).
+The mechanisms are parameterised (window / chunk / pooled-block size, score scale, unit-norm epsilon, rotary table, gate, state
+size, activation kind, router groups, ...) so that another design can list them in another combination; a design is a function
+config.json -> LayeredConfig.
 
 One step function serves prefill, decode and mixed steps: `LayeredModel.forward(step)` takes a flat batch of tokens (prompt
 portions beside single decoded tokens, blazr_b200/batch.py: build_step) and runs every layer once over all of them.  All math
@@ -27,6 +32,32 @@ from .batch import StepArrays
 
 # ---- specs -----------------------------------------------------------------------------------------------------------------
 @dataclass
+class RotarySpec:
+    """rotary positions on the first `dims` dimensions of every q / k head, pairs (2i, 2i + 1); frequency base^(-2i / dims).
+    yarn = (factor, original, fast, slow): frequencies whose wavelength fits `original` positions fewer than `slow` times are divided by
+    `factor`, those that fit more than `fast` times stay, with a linear ramp over the pair index between; cos and sin are scaled
+    by 0.1 ln(factor) + 1."""
+    dims: int
+    base: float
+    yarn: Optional[tuple] = None
+
+    def table(self):
+        """(frequencies float32 [dims / 2], scale of cos and sin)"""
+        import math
+        i = np.arange(self.dims // 2, dtype=np.float64)
+        f = self.base ** (-2.0 * i / self.dims)
+        mscale = 1.0
+        if self.yarn is not None:
+            factor, original, fast, slow = self.yarn
+            at = lambda turns: self.dims * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(self.base))
+            lo, hi = max(math.floor(at(fast)), 0), min(math.ceil(at(slow)), self.dims - 1)
+            ramp = np.clip((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+            f = f / factor * ramp + f * (1.0 - ramp)
+            mscale = 0.1 * math.log(factor) + 1.0
+        return f.astype(np.float32), float(mscale)
+
+
+@dataclass
 class AttentionSpec:
     heads: int
     kv_heads: int
@@ -37,6 +68,9 @@ class AttentionSpec:
     window: int = 0          # > 0: a query sees only the last `window` positions
     qk_unit_norm: bool = True
     gated: bool = True       # one sigmoid gate per head on the output
+    pool: int = 0            # > 0 (with window): blocks of `pool` positions wholly before the window are seen through their mean key / value
+    values_from_keys: bool = False   # no value projection: v = k as projected (before norm and rotation)
+    rot: Optional[RotarySpec] = None
 
 
 @dataclass
@@ -52,16 +86,32 @@ class SsmSpec:
 @dataclass
 class DenseFfSpec:
     ff: int
-    limit: float
+    limit: float = 0.0
     alpha: float = 1.702     # gate activation g * sigmoid(alpha * g)
     up_shift: float = 1.0    # (up + up_shift)
+    act: str = "swish_clamp" # "swish_clamp": min(g, limit) * sigmoid(alpha * g) * (clamp(up) + up_shift); "gelu_tanh": gelu_tanh(g) * up
+
+
+@dataclass
+class MoeFfSpec:
+    """`top` of `experts` small feed-forwards (down(act(up h)), no gate branch) per token, chosen by sigmoid router scores among the experts
+    of the `keep` best of `groups` groups of neighbours, weighted by their scores normalised over the chosen; optionally a shared expert
+    of the same form for every token, times a sigmoid token gate"""
+    experts: int
+    top: int
+    ff: int
+    groups: int = 1
+    keep: int = 1
+    act: str = "relu2"
+    shared_ff: int = 0       # 0: no shared expert
+    shared_gate: bool = True
 
 
 @dataclass
 class LayerSpec:
     kind: str                # "attention" | "ssm"
     mixer: object
-    ff: Optional[DenseFfSpec]
+    ff: Optional[object]     # DenseFfSpec | MoeFfSpec | None
 
 
 @dataclass
@@ -75,6 +125,9 @@ class LayeredConfig:
     canon_taps: int          # taps of the convolution in front of every sublayer
     embed_scale: float
     layers: List[LayerSpec] = field(default_factory=list)
+    layout: str = "streams"  # "streams" | "depth" (see the module text)
+    tied_head: bool = True   # the output projection is the embedding table; False: a tensor "head"
+    depth_average: bool = True   # layout "depth": layer i has weights "l<i>.dwa" [i + 2] over the embedding and the results of layers 0..i
 
 
 class _Workspace:
@@ -96,6 +149,25 @@ class _Workspace:
         self.inner_a = torch.empty((cap, max(1, model.max_inner)), **act)
         self.fin = torch.empty((cap, W), **act)
         self.logits = torch.empty((cap, cfg.vocab), **f32)
+        if cfg.layout == "depth":       # results of the embedding and of every layer but the last (the depth average reads them), second branch
+            self.hist = torch.empty((max(1, len(cfg.layers)), cap, W), **f32)
+            self.xbuf = torch.empty((cap, W), **f32)
+            self.a2 = torch.empty((cap, W), **act)
+            self.y2 = torch.empty((cap, W), **f32)
+        mo = model.moe_dims
+        if mo is not None:              # mixture of experts: router logits, choices, sort, per-pair intermediates
+            E1, top, F = mo
+            i32 = dict(dtype=torch.int32, device=dev)
+            self.moe_z = torch.empty((cap, E1), **f32)
+            self.moe_ids = torch.empty((cap * top,), **i32)
+            self.moe_wts = torch.empty((cap * top,), **f32)
+            self.moe_cnt = torch.zeros((E1,), **i32)
+            self.moe_off = torch.zeros((E1 + 1,), **i32)
+            self.moe_order = torch.empty((cap * top,), **i32)
+            self.moe_slot = torch.empty((cap * top,), **i32)
+            self.moe_act = torch.empty((cap * top, F), **act)
+            self.moe_ys = torch.empty((cap * top, W), **f32)
+            self.moe_sh = torch.empty((cap, W), **f32)
         self.scratch = torch.empty(max(1, model.scratch_floats(cap)), **f32)      # work area: segmented state-space scan, key-split attention
         self.next_ids = torch.empty((cap,), dtype=torch.int32, device=dev)
         # int32 step arrays in one buffer: ids | ent | pos | want | start | slot | pos0 | block_table
@@ -146,25 +218,53 @@ class LayeredModel:
         def hc(pre):    # (in [S], post = out [S] | mix [S, S])
             return vec(pre + "in"), torch.cat([get(pre + "out").float().reshape(-1), get(pre + "mix").float().reshape(-1)]).contiguous().to(dev)
 
+        if cfg.layout not in ("streams", "depth"):
+            raise ValueError(f"unknown residual layout {cfg.layout}")
+        depth = cfg.layout == "depth"
+        if depth and (S != 1 or cfg.canon_taps > 1):
+            raise ValueError("the depth-averaged layout has one residual stream and no carried convolution")
         self.embed = lin("embed")
+        self.head = self.embed if cfg.tied_head else lin("head")
         self.final_norm = vec("final.norm")
-        if tuple(self.embed.shape) != (cfg.vocab, W) or self.final_norm.numel() != W:
-            raise ValueError("embedding / final norm shapes do not fit the configuration")
+        if tuple(self.embed.shape) != (cfg.vocab, W) or tuple(self.head.shape) != (cfg.vocab, W) or self.final_norm.numel() != W:
+            raise ValueError("embedding / head / final norm shapes do not fit the configuration")
         self.ones_in = torch.ones(S, dtype=torch.float32, device=dev)
         self.layers: List[Dict[str, object]] = []
         self.max_proj = self.max_xbc = self.max_inner = 1
-        self.weight_bytes = self.embed.numel() * 2
+        self.moe_dims = None      # (experts + 1, top, expert ff): largest over the layers
+        self.weight_bytes = self.embed.numel() * 2 + (0 if cfg.tied_head else self.head.numel() * 2)
         for i, ls in enumerate(cfg.layers):
             L: Dict[str, object] = {"spec": ls}
             p = f"l{i}."
-            L["norm1"], L["canon1"] = vec(p + "norm1"), vec(p + "canon1")
-            L["hc1_in"], L["hc1_post"] = hc(p + "hc1.")
+            L["norm1"] = vec(p + "norm1")
+            if depth:
+                if L["norm1"].numel() != W:
+                    raise ValueError(f"layer {i}: norm weight does not fit the width")
+                L["dwa"] = vec(p + "dwa") if cfg.depth_average else None      # None: the plain residual sum goes on
+                if L["dwa"] is not None and L["dwa"].numel() != i + 2:
+                    raise ValueError(f"layer {i}: {i + 2} depth weights expected")
+            else:
+                L["canon1"] = vec(p + "canon1")
+                L["hc1_in"], L["hc1_post"] = hc(p + "hc1.")
             m = ls.mixer
             if ls.kind == "attention":
-                names = [p + "mix.q", p + "mix.k", p + "mix.v"] + ([p + "mix.g"] if m.gated else [])
+                names = [p + "mix.q", p + "mix.k"] + ([] if m.values_from_keys else [p + "mix.v"]) + ([p + "mix.g"] if m.gated else [])
                 L["w_in"] = lin(*names)
                 L["w_o"] = lin(p + "mix.o")
-                n_in = m.heads * m.dim + m.kv_heads * (m.dim + m.vdim) + (m.heads if m.gated else 0)
+                if m.values_from_keys and m.vdim != m.dim:
+                    raise ValueError(f"layer {i}: values taken from the keys need vdim == dim")
+                if m.pool > 0 and m.window < 1:
+                    raise ValueError(f"layer {i}: pooled blocks need a window")
+                rot_freq, rot_scale = None, 1.0
+                if m.rot is not None:
+                    if m.rot.dims < 2 or m.rot.dims % 2 or m.rot.dims > m.dim:
+                        raise ValueError(f"layer {i}: rotary dimensions must be even and at most the head size")
+                    fr, rot_scale = m.rot.table()
+                    rot_freq = torch.from_numpy(fr).to(dev)
+                L["rot_freq"] = rot_freq
+                L["desc"] = seqops.attn_desc(m.heads, m.kv_heads, m.dim, m.vdim, m.scale, values_from_keys=m.values_from_keys, gated=m.gated, chunk=m.chunk,
+                                             window=m.window, pool=m.pool, qk_eps=cfg.eps if m.qk_unit_norm else -1.0, rot_freq=rot_freq, rot_scale=rot_scale)
+                n_in = L["desc"].width
                 if tuple(L["w_in"].shape) != (n_in, W) or tuple(L["w_o"].shape) != (W, m.heads * m.vdim):
                     raise ValueError(f"layer {i}: attention tensor shapes do not fit the configuration")
                 self.max_inner = max(self.max_inner, m.heads * m.vdim)
@@ -182,9 +282,38 @@ class LayeredModel:
                 raise ValueError(f"layer {i}: unknown mixer kind {ls.kind}")
             self.max_proj = max(self.max_proj, L["w_in"].shape[0])
             self.weight_bytes += (L["w_in"].numel() + L["w_o"].numel()) * 2
-            if ls.ff is not None:
-                L["norm2"], L["canon2"] = vec(p + "norm2"), vec(p + "canon2")
-                L["hc2_in"], L["hc2_post"] = hc(p + "hc2.")
+            if isinstance(ls.ff, MoeFfSpec):
+                f = ls.ff
+                if f.act not in ("relu2",) or seqops.ACT_KINDS[f.act] in seqops.ACT_GATED:
+                    raise ValueError(f"layer {i}: expert activation {f.act} is not supported")
+                if f.top > f.experts or (f.groups > 1 and (f.experts % f.groups or not 1 <= f.keep <= f.groups or f.keep * (f.experts // f.groups) < f.top)):
+                    raise ValueError(f"layer {i}: router groups / top do not fit the expert count")
+                L["norm2"] = vec(p + "norm2")
+                router = [p + "mlp.router"] + ([p + "mlp.shared.sg"] if f.shared_ff and f.shared_gate else [])
+                L["w_router"] = lin(*router)          # the shared expert's token gate rides as one more row
+                L["w_eup"] = torch.stack([lin(p + f"mlp.e{e}.up") for e in range(f.experts)]).contiguous()
+                L["w_edown"] = torch.stack([lin(p + f"mlp.e{e}.down") for e in range(f.experts)]).contiguous()
+                if tuple(L["w_router"].shape) != (len(router) - 1 + f.experts, W) or tuple(L["w_eup"].shape[1:]) != (f.ff, W) or tuple(L["w_edown"].shape[1:]) != (W, f.ff):
+                    raise ValueError(f"layer {i}: router / expert tensor shapes do not fit the configuration")
+                self.weight_bytes += (L["w_router"].numel() + L["w_eup"].numel() + L["w_edown"].numel()) * 2
+                if f.shared_ff:
+                    L["w_sup"], L["w_sdown"] = lin(p + "mlp.shared.up"), lin(p + "mlp.shared.down")
+                    if tuple(L["w_sup"].shape) != (f.shared_ff, W) or tuple(L["w_sdown"].shape) != (W, f.shared_ff):
+                        raise ValueError(f"layer {i}: shared expert tensor shapes do not fit the configuration")
+                    self.weight_bytes += (L["w_sup"].numel() + L["w_sdown"].numel()) * 2
+                    self.max_inner = max(self.max_inner, f.shared_ff)
+                    self.max_proj = max(self.max_proj, f.shared_ff)
+                md = self.moe_dims or (1, 1, 1)
+                self.moe_dims = (max(md[0], f.experts + 1), max(md[1], f.top), max(md[2], f.ff))
+                if not depth:
+                    raise ValueError("mixture-of-experts feed-forwards are wired into the depth-averaged layout only")
+            elif ls.ff is not None:
+                L["norm2"] = vec(p + "norm2")
+                if not depth:
+                    L["canon2"] = vec(p + "canon2")
+                    L["hc2_in"], L["hc2_post"] = hc(p + "hc2.")
+                if ls.ff.act not in seqops.ACT_KINDS or seqops.ACT_KINDS[ls.ff.act] not in seqops.ACT_GATED:
+                    raise ValueError(f"layer {i}: dense feed-forward activation {ls.ff.act} is not a gated kind")
                 gu = lin(p + "mlp.gate", p + "mlp.up")          # stored with alternating rows (gate j, up j): the pair meets in one warp
                 L["w_gu"] = gu.view(2, ls.ff.ff, W).transpose(0, 1).reshape(2 * ls.ff.ff, W).contiguous()
                 L["w_down"] = lin(p + "mlp.down")
@@ -210,12 +339,17 @@ class LayeredModel:
         for L in self.layers:
             ls = L["spec"]
             m = ls.mixer
-            L["canon1_state"] = torch.zeros((max_seqs, max(hist, 1), cfg.width), **f32)
-            if ls.ff is not None:
-                L["canon2_state"] = torch.zeros((max_seqs, max(hist, 1), cfg.width), **f32)
+            if cfg.layout == "streams":
+                L["canon1_state"] = torch.zeros((max_seqs, max(hist, 1), cfg.width), **f32)
+                if ls.ff is not None:
+                    L["canon2_state"] = torch.zeros((max_seqs, max(hist, 1), cfg.width), **f32)
             if ls.kind == "attention":
                 L["kpool"] = torch.zeros((max(1, num_blocks), block_size, m.kv_heads, m.dim), **f32)
                 L["vpool"] = torch.zeros((max(1, num_blocks), block_size, m.kv_heads, m.vdim), **f32)
+                if m.pool > 0:      # mean key / value of every block of `pool` positions, kept in the page of the block's first position
+                    per_page = -(-block_size // m.pool)
+                    L["kpooled"] = torch.zeros((max(1, num_blocks), per_page, m.kv_heads, m.dim), **f32)
+                    L["vpooled"] = torch.zeros((max(1, num_blocks), per_page, m.kv_heads, m.vdim), **f32)
             else:
                 L["conv_state"] = torch.zeros((max_seqs, max(m.conv - 1, 1), m.heads * m.vdim + 2 * m.groups * m.state), **f32)
                 L["ssm_state"] = torch.zeros((max_seqs, m.heads, m.state, m.vdim), **f32)
@@ -231,9 +365,10 @@ class LayeredModel:
             if L["spec"].kind == "ssm":
                 need = max(need, seqops.ssm_scratch_floats(cap, self.max_seqs, m.heads, m.vdim, m.state))
             else:
-                keys = self.max_blocks * self.block_size
+                ctx = keys = self.max_blocks * self.block_size
                 keys = min(keys, m.chunk) if m.chunk > 0 else keys
                 keys = min(keys, m.window) if m.window > 0 else keys
+                keys += ctx // m.pool if m.pool > 0 else 0
                 key = (m.heads, m.kv_heads, m.vdim, keys)
                 if key not in seen:     # the split count falls as the step grows: the largest need is at some T <= cap
                     seen.add(key)
@@ -241,7 +376,7 @@ class LayeredModel:
         return need
 
     def cache_bytes(self) -> int:
-        keys = ("canon1_state", "canon2_state", "kpool", "vpool", "conv_state", "ssm_state")
+        keys = ("canon1_state", "canon2_state", "kpool", "vpool", "kpooled", "vpooled", "conv_state", "ssm_state")
         return sum(L[k].numel() * 4 for L in self.layers for k in keys if k in L)
 
     def _workspace(self, T: int) -> _Workspace:
@@ -312,6 +447,58 @@ class LayeredModel:
         return ws.logits[:R]
 
     def _run(self, ws: _Workspace, T: int, B: int, R: int, sample: bool, debug_layers: Optional[list]) -> None:
+        if self.cfg.layout == "depth":
+            self._run_depth(ws, T, B, R, sample, debug_layers)
+        else:
+            self._run_streams(ws, T, B, R, sample, debug_layers)
+        if R:
+            seqops.linear(ws.fin[:R], self.head, ws.logits[:R])
+            if sample:
+                seqops.argmax(ws.logits[:R], ws.next_ids[:R])
+
+    def _run_depth(self, ws: _Workspace, T: int, B: int, R: int, sample: bool, debug_layers: Optional[list]) -> None:
+        """parallel layers over one depth-averaged residual stream.  Between two layers one kernel adds the two branches to the layer's
+        input, stores the result for the averages to come, forms the next layer's input and applies both of its layer norms."""
+        cfg, ops = self.cfg, seqops
+        st = self._desc(ws, T, B)
+        hist, xbuf = ws.hist, ws.xbuf[:T]
+        a1, a2, y1, y2 = ws.a[:T], ws.a2[:T], ws.y[:T], ws.y2[:T]
+        x0 = hist[0, :T]
+        ops.embed_streams(self.embed, ws.view("ids"), cfg.embed_scale, x0.view(T, 1, cfg.width))
+        n = len(self.layers)
+        if n:
+            L0 = self.layers[0]
+            ops.depth_norm(x0, a1, L0["norm1"], cfg.eps, out2=a2 if L0["spec"].ff is not None else None, w2=L0.get("norm2"))
+        x_cur = x0
+        for i, L in enumerate(self.layers):
+            ls: LayerSpec = L["spec"]
+            if ls.kind == "attention":
+                self._attention(L, ls.mixer, ws, st, T, a1, y1)
+            else:
+                raise ValueError("the depth-averaged layout is wired for attention mixers")
+            has_ff = ls.ff is not None
+            if isinstance(ls.ff, MoeFfSpec):
+                self._moe_ff(L, ls.ff, ws, T, a2, y2)
+            elif has_ff:
+                self._dense_ff(L, ls.ff, ws, T, a2, y2)
+            upd = dict(y1=y1, y2=y2 if has_ff else None, hist=hist, n_prev=i + 1, dwa=L["dwa"], x_out=xbuf)
+            if i + 1 < n:
+                N = self.layers[i + 1]
+                two = N["spec"].ff is not None
+                ops.depth_norm(x_cur, a1, N["norm1"], cfg.eps, out2=a2 if two else None, w2=N.get("norm2") if two else None, hist_out=hist[i + 1, :T], **upd)
+            elif debug_layers is not None:
+                ops.depth_norm(x_cur, None, None, cfg.eps, **upd)
+                if R:
+                    ops.depth_norm(xbuf, ws.fin[:R], self.final_norm, cfg.eps, rows=ws.view("want")[:R])
+            elif R:
+                ops.depth_norm(x_cur, ws.fin[:R], self.final_norm, cfg.eps, rows=ws.view("want")[:R], **upd)
+            x_cur = xbuf
+            if debug_layers is not None:
+                debug_layers.append(xbuf.cpu())
+        if not n and R:
+            ops.depth_norm(x0, ws.fin[:R], self.final_norm, cfg.eps, rows=ws.view("want")[:R])
+
+    def _run_streams(self, ws: _Workspace, T: int, B: int, R: int, sample: bool, debug_layers: Optional[list]) -> None:
         cfg = self.cfg
         ops = seqops
         st = self._desc(ws, T, B)
@@ -340,17 +527,14 @@ class LayeredModel:
                 debug_layers.append(Xn.sum(1).cpu())
         if R:
             ops.hc_norm(X, y_prev, post_prev, self.ones_in, self.final_norm, cfg.norm_groups, cfg.eps, ws.fin[:R], rows=ws.view("want")[:R])
-            ops.linear(ws.fin[:R], self.embed, ws.logits[:R])
-            if sample:
-                ops.argmax(ws.logits[:R], ws.next_ids[:R])
 
     def _attention(self, L, m: AttentionSpec, ws: _Workspace, st, T: int, a: torch.Tensor, y: torch.Tensor) -> None:
         n_in = L["w_in"].shape[0]
         qkvg = ws.proj[:T, :n_in]
         seqops.linear(a, L["w_in"], qkvg)
-        seqops.attn_prep(qkvg, st, L["kpool"], L["vpool"], m.heads, m.kv_heads, m.dim, m.vdim, self.cfg.eps if m.qk_unit_norm else -1.0)
+        seqops.attn_prep_ex(qkvg, st, L["desc"], L["kpool"], L["vpool"], L.get("kpooled"), L.get("vpooled"))
         o = ws.inner_a.view(-1)[:T * m.heads * m.vdim].view(T, m.heads * m.vdim)
-        seqops.attn(qkvg, st, L["kpool"], L["vpool"], m.heads, m.kv_heads, m.dim, m.vdim, m.scale, m.chunk, m.window, m.gated, o, ws.scratch)
+        seqops.attn_ex(qkvg, st, L["desc"], L["kpool"], L["vpool"], o, ws.scratch, L.get("kpooled"), L.get("vpooled"))
         seqops.linear(o, L["w_o"], y)
 
     def _ssm(self, L, m: SsmSpec, ws: _Workspace, st, T: int, a: torch.Tensor, y: torch.Tensor) -> None:
@@ -368,10 +552,44 @@ class LayeredModel:
 
     def _dense_ff(self, L, f: DenseFfSpec, ws: _Workspace, T: int, a: torch.Tensor, y: torch.Tensor) -> None:
         act = ws.inner_a.view(-1)[:T * f.ff].view(T, f.ff)
-        if T <= 8 or (T >= seqops.TC_MIN_ROWS and seqops.tc_usable(a, a.shape[1])):     # projection and activation in one kernel
-            seqops.linear_gated(a, L["w_gu"], f.limit, f.alpha, f.up_shift, act)
-        else:
-            gu = ws.proj[:T, :2 * f.ff]
-            seqops.linear(a, L["w_gu"], gu)
-            seqops.gated_act(gu, f.limit, f.alpha, f.up_shift, act, interleaved=True)
+        self._proj_act(ws, T, a, L["w_gu"], seqops.ACT_KINDS[f.act], act, f.limit, f.alpha, f.up_shift)
         seqops.linear(act, L["w_down"], y)
+
+    def _proj_act(self, ws: _Workspace, T: int, a: torch.Tensor, w: torch.Tensor, kind: int, out: torch.Tensor, limit: float = 0.0, alpha: float = 0.0,
+                  shift: float = 0.0) -> None:
+        """out = act(a . w^T): projection and activation in one kernel where a fused path takes the step, else product + activation"""
+        if T <= 8 or (T >= seqops.TC_MIN_ROWS and seqops.tc_usable(a, a.shape[1])):
+            seqops.linear_act(a, w, kind, out, limit, alpha, shift)
+        else:
+            z = ws.proj[:T, :w.shape[0]]
+            seqops.linear(a, w, z)
+            seqops.act(z, kind, out, limit, alpha, shift)
+
+    MOE_ROW_PAIRS = 64      # up to this many (token, choice) pairs the experts' weights are streamed per pair; more: tiles over sorted pairs
+
+    def _moe_ff(self, L, f: "MoeFfSpec", ws: _Workspace, T: int, a: torch.Tensor, y: torch.Tensor) -> None:
+        ops = seqops
+        E, top = f.experts, f.top
+        gated_shared = bool(f.shared_ff and f.shared_gate)
+        z = ws.moe_z[:T, :L["w_router"].shape[0]]
+        ops.linear(a, L["w_router"], z)
+        pairs = T * top
+        rows_form = pairs <= self.MOE_ROW_PAIRS
+        ops.moe_route(z, E, f.groups, f.keep, top, ws.moe_ids, ws.moe_wts, None if rows_form else ws.moe_cnt)
+        kind = ops.ACT_KINDS[f.act]
+        mid = ws.moe_act.view(-1)[:pairs * f.ff].view(pairs, f.ff)
+        ys = ws.moe_ys[:pairs]
+        if rows_form:
+            order = offs = slot = None
+        else:
+            order, offs, slot = ws.moe_order, ws.moe_off, ws.moe_slot
+            ops.moe_sort(ws.moe_ids, pairs, E, ws.moe_cnt, offs, order, slot)
+        ops.moe_linear(a, top, L["w_eup"], ws.moe_ids, order, offs, pairs, kind, mid)
+        ops.moe_linear(mid, 0, L["w_edown"], ws.moe_ids, order, offs, pairs, ops.ACT_NONE, ys)
+        sh = None
+        if f.shared_ff:
+            smid = ws.inner_a.view(-1)[:T * f.shared_ff].view(T, f.shared_ff)
+            self._proj_act(ws, T, a, L["w_sup"], kind, smid)
+            sh = ws.moe_sh[:T]
+            ops.linear(smid, L["w_sdown"], sh)
+        ops.moe_combine(ys, ws.moe_wts, slot, T, top, sh, z[:, E] if gated_shared else None, y)

@@ -12,7 +12,7 @@ from __future__ import annotations
 import os
 from typing import Callable, Dict
 
-from . import fenorax
+from . import fenorax, gemosun
 from .layered import LayeredConfig, LayeredModel
 
 LAYERED: Dict[str, Callable[[dict], LayeredConfig]] = {}
@@ -24,6 +24,7 @@ def register_layered(name: str, parse: Callable[[dict], LayeredConfig]) -> None:
 
 
 register_layered(fenorax.ARCHITECTURE, fenorax.parse_config)
+register_layered(gemosun.ARCHITECTURE, gemosun.parse_config)
 
 
 class UnknownArchitecture(ValueError):

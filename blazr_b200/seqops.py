@@ -23,13 +23,18 @@ LIB_PATH = os.environ.get("B200SEQ_LIB") or os.path.join(_HERE, "lib", "libb200s
 
 F32, BF16 = 0, 2
 CONV_RESIDUAL, CONV_SILU = 1, 2
+ACT_SWISH_CLAMP, ACT_GELU_TANH, ACT_RELU2 = 0, 1, 2   # gated: clamped swish, tanh-gelu gate; plain: squared relu
+ACT_NONE = -1
+ACT_KINDS = {"swish_clamp": ACT_SWISH_CLAMP, "gelu_tanh": ACT_GELU_TANH, "relu2": ACT_RELU2}
+ACT_GATED = (ACT_SWISH_CLAMP, ACT_GELU_TANH)
 PATH_AUTO, PATH_ROWS, PATH_TILED, PATH_TC = 0, 1, 2, 3
 TC_MIN_ROWS = 32   # b200seq_linear's automatic choice takes the tensor-core path from this many rows
 _DT = {torch.float32: F32, torch.bfloat16: BF16}
 
 EXPORTS = ["b200seq_last_error", "b200seq_version", "b200seq_launch_count", "b200seq_error_flags", "b200seq_embed_streams", "b200seq_hc_norm", "b200seq_hc_norm_conv",
            "b200seq_causal_conv", "b200seq_group_rmsnorm", "b200seq_gated_act", "b200seq_linear", "b200seq_linear_gated", "b200seq_attn_prep", "b200seq_attn", "b200seq_attn_scratch_floats",
-           "b200seq_ssm_scan", "b200seq_ssm_scratch_floats", "b200seq_argmax"]
+           "b200seq_ssm_scan", "b200seq_ssm_scratch_floats", "b200seq_argmax", "b200seq_linear_act", "b200seq_act", "b200seq_depth_norm", "b200seq_attn_prep_ex",
+           "b200seq_attn_ex", "b200seq_moe_route", "b200seq_moe_sort", "b200seq_moe_linear", "b200seq_moe_combine"]
 
 
 class SeqError(RuntimeError):
@@ -42,6 +47,26 @@ class StepDesc(C.Structure):
     """b200seq_step: device pointers of one step's int32 arrays (see include/b200seq.h)"""
     _fields_ = [("tok_ent", C.c_void_p), ("tok_pos", C.c_void_p), ("ent_start", C.c_void_p), ("ent_slot", C.c_void_p), ("ent_pos0", C.c_void_p),
                 ("block_table", C.c_void_p), ("T", C.c_int32), ("B", C.c_int32), ("max_blocks", C.c_int32), ("block_size", C.c_int32)]
+
+
+class AttnDesc(C.Structure):
+    """b200seq_attn_desc: sizes, columns of the projection row and mask / rotation constants of one attention layer"""
+    _fields_ = [("H", C.c_int32), ("G", C.c_int32), ("D", C.c_int32), ("V", C.c_int32), ("q_col", C.c_int32), ("k_col", C.c_int32), ("v_col", C.c_int32),
+                ("gate_col", C.c_int32), ("scale", C.c_float), ("chunk", C.c_int32), ("window", C.c_int32), ("pool", C.c_int32), ("qk_eps", C.c_float),
+                ("rot_dims", C.c_int32), ("rot_freq", C.c_void_p), ("rot_scale", C.c_float)]
+
+
+def attn_desc(H: int, G: int, D: int, V: int, scale: float, *, values_from_keys: bool = False, gated: bool = True, chunk: int = 0, window: int = 0, pool: int = 0,
+              qk_eps: float = -1.0, rot_freq: Optional[torch.Tensor] = None, rot_scale: float = 1.0) -> "AttnDesc":
+    """descriptor for a projection row laid out q | k | v | gate (v absent when the values are the keys, gate absent when not gated);
+    rot_freq: device f32 [rot_dims / 2] (the caller keeps it alive)"""
+    k_col = H * D
+    v_col = k_col if values_from_keys else k_col + G * D
+    end = v_col + (G * D if values_from_keys else G * V)
+    d = AttnDesc(H, G, D, V, 0, k_col, v_col, end if gated else -1, scale, chunk, window, pool, qk_eps, 2 * rot_freq.numel() if rot_freq is not None else 0,
+                 rot_freq.data_ptr() if rot_freq is not None else None, rot_scale)
+    d.width = end + (H if gated else 0)
+    return d
 
 
 def _stale() -> bool:
@@ -203,6 +228,89 @@ def linear_gated(x: torch.Tensor, w_il: torch.Tensor, limit: float, alpha: float
     assert w_il.dtype == torch.bfloat16 and w_il.is_contiguous() and tuple(w_il.shape) == (2 * F, K) and out.shape[0] == M
     _check(lib().b200seq_linear_gated(_p(x), _DT[x.dtype], C.c_int64(ldx), _p(w_il), M, F, K, C.c_float(limit), C.c_float(alpha), C.c_float(up_shift), _p(out),
                                       _DT[out.dtype], C.c_int64(ldo), _st(x)))
+
+
+@_timed
+def linear_act(x: torch.Tensor, w: torch.Tensor, act: int, out: torch.Tensor, limit: float = 0.0, alpha: float = 0.0, shift: float = 0.0):
+    """out = act(x . w^T) in one kernel; w bf16 [N, K]; gated kinds (rows of w alternate gate / up) give out [M, N / 2], plain kinds [M, N]
+    (up to 8 rows: any activation type; more: the tensor-core path, bf16 activations only)"""
+    M, K, ldx = _rows2d(x)
+    _, F, ldo = _rows2d(out)
+    N = w.shape[0]
+    assert w.dtype == torch.bfloat16 and w.is_contiguous() and w.shape[1] == K and out.shape[0] == M and F == (N // 2 if act in ACT_GATED else N)
+    _check(lib().b200seq_linear_act(_p(x), _DT[x.dtype], C.c_int64(ldx), _p(w), M, N, K, act, C.c_float(limit), C.c_float(alpha), C.c_float(shift), _p(out),
+                                    _DT[out.dtype], C.c_int64(ldo), _st(x)))
+
+
+@_timed
+def act(z: torch.Tensor, kind: int, out: torch.Tensor, limit: float = 0.0, alpha: float = 0.0, shift: float = 0.0):
+    """the same activation on a product that is in memory (z f32 [T, N]; gated kinds read interleaved pairs)"""
+    T, N, ldz = _rows2d(z)
+    _, _, ldo = _rows2d(out)
+    _check(lib().b200seq_act(_p(z), C.c_int64(ldz), T, N, kind, C.c_float(limit), C.c_float(alpha), C.c_float(shift), _p(out), _DT[out.dtype], C.c_int64(ldo), _st(z)))
+
+
+@_timed
+def depth_norm(x_cur: torch.Tensor, out1: Optional[torch.Tensor], w1: Optional[torch.Tensor], eps: float, *, out2: Optional[torch.Tensor] = None,
+               w2: Optional[torch.Tensor] = None, y1: Optional[torch.Tensor] = None, y2: Optional[torch.Tensor] = None, hist: Optional[torch.Tensor] = None,
+               n_prev: int = 0, dwa: Optional[torch.Tensor] = None, hist_out: Optional[torch.Tensor] = None, x_out: Optional[torch.Tensor] = None,
+               rows: Optional[torch.Tensor] = None):
+    """residual sum of a parallel layer (x_cur + (y1 + y2)), learned average over the results of all layers so far (hist [>= n_prev, cap, W] holds the
+    earlier ones, dwa [n_prev + 1]), and up to two weighted layer norms of the outcome; rows: only these token rows (outputs are row-compact)"""
+    W = x_cur.shape[-1]
+    R = x_cur.shape[0] if rows is None else rows.numel()
+    o = out1 if out1 is not None else out2
+    _check(lib().b200seq_depth_norm(_p(hist), C.c_int64(hist.stride(0) if hist is not None else 0), n_prev, _p(dwa), _p(x_cur), _p(y1), _p(y2), _p(hist_out), _p(x_out), W,
+                                    C.c_float(eps), _p(w1), _p(w2), _p(rows), R, _p(out1), _p(out2), _DT[o.dtype] if o is not None else F32, _st(x_cur)))
+
+
+@_timed
+def attn_prep_ex(proj: torch.Tensor, step: "StepDesc", d: "AttnDesc", kpool: torch.Tensor, vpool: torch.Tensor, kpooled: Optional[torch.Tensor] = None,
+                 vpooled: Optional[torch.Tensor] = None):
+    _, _, ld = _rows2d(proj)
+    _check(lib().b200seq_attn_prep_ex(_p(proj), C.c_int64(ld), C.byref(step), C.byref(d), _p(kpool), _p(vpool), _p(kpooled), _p(vpooled), _st(proj)))
+
+
+@_timed
+def attn_ex(proj: torch.Tensor, step: "StepDesc", d: "AttnDesc", kpool: torch.Tensor, vpool: torch.Tensor, out: torch.Tensor, scratch: Optional[torch.Tensor] = None,
+            kpooled: Optional[torch.Tensor] = None, vpooled: Optional[torch.Tensor] = None):
+    _, _, ld = _rows2d(proj)
+    assert out.is_contiguous() and (scratch is None or (scratch.dtype == torch.float32 and scratch.is_contiguous()))
+    _check(lib().b200seq_attn_ex(_p(proj), C.c_int64(ld), C.byref(step), C.byref(d), _p(kpool), _p(vpool), _p(kpooled), _p(vpooled), _p(out), _DT[out.dtype], _p(scratch),
+                                 C.c_size_t(scratch.numel() if scratch is not None else 0), _st(proj)))
+
+
+@_timed
+def moe_route(z: torch.Tensor, E: int, groups: int, keep: int, top: int, ids: torch.Tensor, wts: torch.Tensor, counts: Optional[torch.Tensor]):
+    """z f32 [T, >= E] router logits -> ids int32 [T, top], wts f32 [T, top], counts int32 [E]"""
+    T, _, ldz = _rows2d(z)
+    assert ids.dtype == torch.int32 and wts.dtype == torch.float32 and ids.is_contiguous() and wts.is_contiguous() and ids.numel() >= T * top
+    _check(lib().b200seq_moe_route(_p(z), C.c_int64(ldz), T, E, groups, keep, top, _p(ids), _p(wts), _p(counts), _st(z)))
+
+
+@_timed
+def moe_sort(ids: torch.Tensor, pairs: int, E: int, counts: torch.Tensor, offs: torch.Tensor, order: torch.Tensor, slot_of: torch.Tensor):
+    _check(lib().b200seq_moe_sort(_p(ids), pairs, E, _p(counts), _p(offs), _p(order), _p(slot_of), _st(ids)))
+
+
+@_timed
+def moe_linear(x: torch.Tensor, x_div: int, w: torch.Tensor, ids: torch.Tensor, order: Optional[torch.Tensor], offs: Optional[torch.Tensor], pairs: int, act: int,
+               out: torch.Tensor):
+    """one projection of every (token, choice) pair through its expert's weight; w bf16 [E, N, K]; out [pairs, N] (f32 when act is ACT_NONE)"""
+    _, K, ldx = _rows2d(x)
+    _, N, ldo = _rows2d(out)
+    E = w.shape[0]
+    assert w.dtype == torch.bfloat16 and w.is_contiguous() and tuple(w.shape[1:]) == (N, K) and out.shape[0] >= pairs
+    _check(lib().b200seq_moe_linear(_p(x), _DT[x.dtype], C.c_int64(ldx), x_div, _p(w), _p(ids), _p(order), _p(offs), pairs, E, N, K, act, _p(out), _DT[out.dtype],
+                                    C.c_int64(ldo), _st(x)))
+
+
+@_timed
+def moe_combine(ys: torch.Tensor, wts: torch.Tensor, slot_of: Optional[torch.Tensor], T: int, top: int, shared: Optional[torch.Tensor], gate_z: Optional[torch.Tensor],
+                y: torch.Tensor):
+    W = y.shape[1]
+    assert ys.is_contiguous() and y.is_contiguous() and (shared is None or shared.is_contiguous())
+    _check(lib().b200seq_moe_combine(_p(ys), _p(wts), _p(slot_of), T, top, W, _p(shared), _p(gate_z), C.c_int64(gate_z.stride(0) if gate_z is not None else 0), _p(y), _st(y)))
 
 
 def tc_usable(x: torch.Tensor, K: int) -> bool:

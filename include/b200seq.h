@@ -129,6 +129,82 @@ size_t b200seq_ssm_scratch_floats(int T, int B, int H, int V, int N);
 int b200seq_ssm_scan(const float* proj, int64_t ldp, int z0, int dt0, const float* xbc, int64_t ldx, const float* A_log, const float* Dp, const float* dt_bias,
                      float* state, const b200seq_step* st, int H, int V, int N, int G, float* out, float* scratch, size_t scratch_floats, void* stream);
 
+/* ---- activations of a projection ------------------------------------------------------------------------------------------------
+ * gated kinds take a stacked gate|up product whose rows alternate (gate j, up j) and give F = N / 2 outputs:
+ *   B200SEQ_ACT_SWISH_CLAMP  g = min(gate, limit), u = clamp(up, -limit, limit): g * sigmoid(alpha * g) * (u + shift)
+ *   B200SEQ_ACT_GELU_TANH    0.5 g (1 + tanh(sqrt(2 / pi) (g + 0.044715 g^3))) * up
+ * plain kinds give N outputs:
+ *   B200SEQ_ACT_RELU2        max(z, 0)^2 */
+#define B200SEQ_ACT_SWISH_CLAMP 0
+#define B200SEQ_ACT_GELU_TANH 1
+#define B200SEQ_ACT_RELU2 2
+
+/* out = act(x . w^T), the product itself never reaches memory.  w: bf16 [N, K]; out [M, N / 2] (gated kinds) or [M, N] (plain kinds) in
+ * out_dtype, row stride ldo.  M <= 8: weight-streaming rows (f32 or bf16 activations); more rows: the tensor-core path, which needs bf16
+ * activations, K % 8 == 0 and 16-byte aligned rows (B200SEQ_ERR_UNSUPPORTED otherwise).  b200seq_linear_gated is kind SWISH_CLAMP. */
+int b200seq_linear_act(const void* x, int x_dtype, int64_t ldx, const void* w_bf16, int M, int N, int K, int act, float limit, float alpha, float shift,
+                       void* out, int out_dtype, int64_t ldo, void* stream);
+/* the same activation applied to a product that is in memory: z f32 [T, N] (stride ldz); gated kinds read interleaved pairs */
+int b200seq_act(const float* z, int64_t ldz, int T, int N, int act, float limit, float alpha, float shift, void* out, int out_dtype, int64_t ldo, void* stream);
+
+/* ---- depth-averaged residual + layer norm ---------------------------------------------------------------------------------------------
+ * One residual stream whose layer inputs are learned averages over depth: with X_0 the embedding and X_(i+1) = x_i + y1 + y2 the result of
+ * layer i (x_i = what layer i read), the next layer reads x_(i+1) = sum_(j <= i + 1) dwa[j] X_j.  One kernel, one block per row r
+ * (token t = rows ? rows[r] : r), does what lies between two layers:
+ *   if y1:   X_new = x_cur[t] + (y1[t] + y2[t])        (y2 may be null)
+ *            hist_out[t] <- X_new                      (if hist_out: layer i stores X_(i+1) for the layers after it)
+ *            x = dwa ? sum_(j < n_prev) dwa[j] * hist[j * hist_stride + t * W] + dwa[n_prev] * X_new : X_new;   x_out[t] <- x
+ *   else     x = x_cur[t]
+ *   out1[r] = layer_norm(x) * w1, out2[r] = layer_norm(x) * w2   (each optional; (x - mean) / sqrt(var + eps), biased variance, no bias)
+ * Everything in f32; out1 / out2 in out_dtype.  x_out may be x_cur. */
+int b200seq_depth_norm(const float* hist, int64_t hist_stride, int n_prev, const float* dwa, const float* x_cur, const float* y1, const float* y2,
+                       float* hist_out, float* x_out, int W, float eps, const float* w1, const float* w2, const int32_t* rows, int R, void* out1, void* out2,
+                       int out_dtype, void* stream);
+
+/* ---- attention, general form ------------------------------------------------------------------------------------------------------------
+ * Columns of the projection row: q at q_col (H*D), k at k_col (G*D), v at v_col (G*V; v_col == k_col: the values are the keys as projected,
+ * before norm and rotation; needs V == D), one gate logit per query head at gate_col (< 0: no gate).
+ * prep, in this order: unit-RMS q and k (qk_eps >= 0); rotation of the first rot_dims dimensions of every q and k head (rot_dims > 0):
+ * the pair (2i, 2i+1) at position p turns by the angle p * rot_freq[i] and is multiplied by rot_scale (rot_freq: device f32 [rot_dims / 2]);
+ * k and v go to the pool; when pool > 0 every block of `pool` positions that the step completes gets its mean key and mean value (of the
+ * pool's rows, summed in position order) written to kpooled / vpooled: [blocks][pooled_per_page][G][D or V] with
+ * pooled_per_page = ceil(block_size / pool), block b of a sequence lives in the page of its first position.
+ * attend: as b200seq_attn; with pool > 0 (needs window > 0) position i also sees, in the same soft-max, the pooled key and value of every
+ * block b with b * pool + pool - 1 <= i - window. */
+typedef struct b200seq_attn_desc {
+    int32_t H, G, D, V;
+    int32_t q_col, k_col, v_col, gate_col;
+    float scale;
+    int32_t chunk, window, pool;
+    float qk_eps;
+    int32_t rot_dims;
+    const float* rot_freq;
+    float rot_scale;
+} b200seq_attn_desc;
+int b200seq_attn_prep_ex(float* proj, int64_t ld, const b200seq_step* st, const b200seq_attn_desc* d, float* kpool, float* vpool, float* kpooled, float* vpooled,
+                         void* stream);
+int b200seq_attn_ex(const float* proj, int64_t ld, const b200seq_step* st, const b200seq_attn_desc* d, const float* kpool, const float* vpool,
+                    const float* kpooled, const float* vpooled, void* out, int out_dtype, float* scratch, size_t scratch_floats, void* stream);
+
+/* ---- mixture of experts -------------------------------------------------------------------------------------------------------------------
+ * route: z f32 [T, >= E] (stride ldz) router logits; s = sigmoid(z).  Experts form `groups` equal groups of neighbours; a group's score is
+ * the sum of its two largest s (of its one, when groups == E); only experts of the `keep` best groups can be chosen (groups <= 1: all).
+ * The `top` largest s among those are chosen (ties: the lower index), ids[t][j] in falling order of s, wts[t][j] = s / (sum of the chosen s
+ * + 1e-20).  counts[E] receives how many (token, choice) pairs every expert got.
+ * sort: the pairs p = t * top + j ordered by expert (stable): offs[E + 1] prefix sums, sorted[slot] = p, slot_of[p] = slot. */
+int b200seq_moe_route(const float* z, int64_t ldz, int T, int E, int groups, int keep, int top, int32_t* ids, float* wts, int32_t* counts, void* stream);
+int b200seq_moe_sort(const int32_t* ids, int pairs, int E, const int32_t* counts, int32_t* offs, int32_t* sorted, int32_t* slot_of, void* stream);
+/* One projection of every pair through its expert's weight: w bf16 [E][N][K].  Row r of the result belongs to pair p = sorted ? sorted[r] : r
+ * (sorted + offs from b200seq_moe_sort: tiles of one expert's rows; null: one launch row per pair, weights streamed, for few pairs).
+ * The input row of row r is x[(x_div > 0 ? p / x_div : r)] (x_div = top gathers the token's activations; 0: x is already laid out like the
+ * result).  act: -1 none (out f32) or a plain activation kind (out in out_dtype).  out [pairs, N], stride ldo. */
+int b200seq_moe_linear(const void* x, int x_dtype, int64_t ldx, int x_div, const void* w_bf16, const int32_t* ids, const int32_t* sorted, const int32_t* offs,
+                       int pairs, int E, int N, int K, int act, void* out, int out_dtype, int64_t ldo, void* stream);
+/* y[t] = sum_j wts[t][j] * ys[slot_of ? slot_of[t * top + j] : t * top + j] (j ascending) + (shared ? sigmoid(gate_z[t * ldg]) * shared[t] : 0)
+ * gate_z null with shared: the shared branch is added as it is.  ys, shared, y: f32 [., W]. */
+int b200seq_moe_combine(const float* ys, const float* wts, const int32_t* slot_of, int T, int top, int W, const float* shared, const float* gate_z, int64_t ldg,
+                        float* y, void* stream);
+
 /* ids[r] = argmax_v logits[r][v] (first maximum) */
 int b200seq_argmax(const float* logits, int R, int V, int32_t* ids, void* stream);
 
