@@ -1,0 +1,331 @@
+"""Gemosun models end to end through the registry, the engine and its cache: small configurations with random weights, compared
+with the plain float64 restatement (tests/gemosun_oracle.py) of whole sequences.  Sizes are chosen unlike each other on purpose:
+head sizes that are no multiple of four, as many key heads as query heads and one key head for all, rotation of a part of a head
+and of the whole head, with and without frequency scaling, windows of one position, pooled blocks of one position, blocks that do
+not divide a cache page and blocks larger than one, layers without feed-forward, experts without groups or without a shared one."""
+import copy
+
+import numpy as np
+import pytest
+import torch
+
+import gemosun_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+YARN = {"factor": 3.0, "original": 64, "fast": 8.0, "slow": 1.5}
+
+
+def att(dim=16, heads=4, kv=2, scale=0.3, size=24, pool=4, rot=8, base=100.0, yarn=YARN, mlp=None):
+    m = {"dim": dim, "vdim": dim, "heads": heads, "kv_heads": kv, "scale": scale}
+    if size:
+        m["mask"] = {"size": size}
+        if pool:
+            m["mask"]["pool"] = pool
+    if rot:
+        m["rot"] = {"dims": rot, "base": base}
+        if yarn:
+            m["rot"]["scaling"] = dict(yarn)
+    return {"type": "attention", "mixer": m, "mlp": mlp}
+
+
+def dense(ff=40):
+    return {"kind": "dense", "ff": ff}
+
+
+def moe(experts=8, top=2, ff=24, groups=(4, 2), shared=16):
+    r = {"experts": experts, "top": top}
+    if groups:
+        r["groups"] = {"count": groups[0], "keep": groups[1]}
+    m = {"kind": "moe", "expert": {"ff": ff}, "router": r}
+    if shared:
+        m["shared"] = {"ff": shared}
+    return m
+
+
+def config(layers, vocab=61, width=48, eps=1e-5):
+    return {"architecture": "Gemosun", "vocab": vocab, "width": width, "norm": {"eps": eps}, "layers": layers}
+
+
+CONFIGS = {
+    "mixed": config([att(mlp=dense()), att(size=7, pool=3, mlp=moe()), att(size=9, pool=0, rot=16, yarn=None), att(size=12, pool=32, mlp=moe(groups=None, shared=0))]),
+    "odd": config([att(dim=10, heads=3, kv=3, size=1, pool=1, rot=10, yarn=None, scale=0.4, mlp=moe(experts=6, top=3, ff=20, groups=(3, 2), shared=12)),
+                   att(dim=10, heads=3, kv=3, size=5, pool=5, rot=4, scale=0.4, mlp=dense(36)),
+                   att(dim=6, heads=2, kv=1, size=0, pool=0, rot=0, scale=0.5, mlp=moe(experts=5, top=1, ff=8, groups=(5, 3), shared=8))], vocab=33, width=44, eps=1e-3),
+    "wide": config([att(dim=32, heads=6, kv=1, size=16, pool=16, rot=32, base=5000.0, scale=0.11, mlp=moe(experts=16, top=4, ff=32, groups=(2, 1), shared=32)),
+                    att(dim=32, heads=6, kv=2, size=40, pool=8, rot=12, scale=0.11, mlp=dense(72))], vocab=130, width=96),
+}
+
+
+class Case:
+    def __init__(self, name, tmp, dtype):
+        from blazr_b200 import registry
+        self.cfg = copy.deepcopy(CONFIGS[name])
+        self.P = O.random_model(self.cfg, seed=11)
+        O.write_checkpoint(str(tmp), self.cfg, self.P)
+        self.model = registry.load_model(str(tmp), "cuda:0", dtype)
+        self._ref = {}
+
+    def engine(self, **kw):
+        from blazr_b200.engine import Engine
+        return Engine(self.model, **kw)
+
+    def ref(self, tokens):
+        key = tuple(tokens)
+        if key not in self._ref:
+            self._ref[key] = O.forward(self.cfg, self.P, list(tokens))
+        return self._ref[key]
+
+
+@pytest.fixture(scope="module")
+def cases(tmp_path_factory):
+    if not torch.cuda.is_available():
+        pytest.skip("no GPU")
+    made = {}
+
+    def get(name, dtype="float32"):
+        if (name, dtype) not in made:
+            made[(name, dtype)] = Case(name, tmp_path_factory.mktemp(f"{name}_{dtype}"), dtype)
+        return made[(name, dtype)]
+    return get
+
+
+def toks(n, vocab, seed):
+    return torch.randint(0, vocab, (n,), generator=torch.Generator().manual_seed(seed)).tolist()
+
+
+def row_errors(got, ref):
+    d = torch.as_tensor(got).double() - ref.double()
+    d = d - d.mean(-1, keepdim=True)
+    return d.pow(2).mean(-1).sqrt() / ref.double().std()
+
+
+def err(got, ref):
+    return row_errors(got, ref).max().item()
+
+
+def err16(got, ref):
+    """bfloat16 mode: a router choice between two experts whose scores differ by less than the rounding of the activations may fall the
+    other way at a few positions, so the bound is on the bulk of the rows (median, and nine rows in ten), not on the worst one"""
+    e = row_errors(got, ref)
+    return max(e.median().item() * 2, e.quantile(0.9).item())
+
+
+TOL32, TOL16 = 5e-5, 1e-1
+
+
+@pytest.mark.parametrize("name", list(CONFIGS))
+def test_whole_prompt_and_layers(cases, name):
+    c = cases(name)
+    t = toks(53, c.cfg["vocab"], 1)
+    eng = c.engine(max_tokens=64, max_seqs=2)
+    got = eng.run_entries([{"id": "a", "tokens": t, "want": list(range(53))}], ["a"])
+    assert err(got, c.ref(t)) < TOL32
+    from blazr_b200.batch import StepEntry, build_step
+    seq = eng.cache.admit("b")
+    eng.cache.reserve(seq, len(t))
+    dbg = []
+    c.model.forward(build_step([StepEntry(t, 0, seq.slot, seq.blocks, [0])], eng.cache.block_size), debug_layers=dbg)
+    outs = []
+    O.forward(c.cfg, c.P, t, layer_out=outs)
+    assert len(dbg) == len(outs)
+    for g, r in zip(dbg, outs):
+        assert (g.double() - r).abs().max().item() < 2e-5 * r.abs().max().item()
+
+
+@pytest.mark.parametrize("name", ["mixed", "wide"])
+def test_bfloat16_mode_stays_close(cases, name):
+    """a portion long enough for the tensor-core paths (plain, gated and squared-relu epilogues), then single tokens"""
+    c = cases(name, "bfloat16")
+    t = toks(100, c.cfg["vocab"], 2)
+    eng = c.engine(max_tokens=112, max_seqs=1)
+    got = eng.run_entries([{"id": "a", "tokens": t[:70], "want": list(range(70))}], [])
+    assert err16(got, c.ref(t)[:70]) < TOL16
+    rows = [eng.run_entries([{"id": "a", "tokens": [t[i]], "want": [0]}], [])[0] for i in range(70, 100)]
+    assert err16(np.stack(rows), c.ref(t)[70:100]) < TOL16
+
+
+@pytest.mark.parametrize("name", list(CONFIGS))
+def test_prefill_then_token_by_token(cases, name):
+    """long decoding: the decoded tokens cross window edges, pooled-block edges and page borders"""
+    c = cases(name)
+    t = toks(100, c.cfg["vocab"], 3)
+    ref = c.ref(t)
+    eng = c.engine(max_tokens=112, max_seqs=1)
+    got = [eng.run_entries([{"id": "a", "tokens": t[:9], "want": [0, 8]}], [])]
+    assert err(got[0], ref[[0, 8]]) < TOL32
+    for i in range(9, 100):
+        got = eng.run_entries([{"id": "a", "tokens": [t[i]], "want": [0]}], [])
+        assert err(got, ref[i:i + 1]) < TOL32, f"decoded position {i}"
+    assert eng.cache.live["a"].n_tokens == 100
+
+
+def test_decode_from_the_very_first_token(cases):
+    c = cases("odd")
+    t = toks(14, c.cfg["vocab"], 4)
+    ref = c.ref(t)
+    eng = c.engine(max_tokens=16, max_seqs=1)
+    for i in range(14):
+        got = eng.run_entries([{"id": "a", "tokens": [t[i]], "want": [0]}], [])
+        assert err(got, ref[i:i + 1]) < TOL32, f"position {i}"
+
+
+@pytest.mark.parametrize("name,sizes", [("mixed", [2, 3, 2, 17, 1, 24, 2, 2, 30, 5]), ("wide", [15, 2, 16, 1, 1, 33, 2, 18, 40]), ("odd", [1, 2, 4, 5, 6, 50, 20])])
+def test_portions_of_changing_size(cases, name, sizes):
+    """portions cut in the middle of pages, windows and pooled blocks; a block's mean may be completed by a two-token portion"""
+    c = cases(name)
+    n = sum(sizes)
+    t = toks(n, c.cfg["vocab"], 5)
+    ref = c.ref(t)
+    eng = c.engine(max_tokens=-(-n // 16) * 16, max_seqs=1)
+    lo = 0
+    for s in sizes:
+        got = eng.run_entries([{"id": "a", "tokens": t[lo:lo + s], "want": list(range(s))}], [])
+        assert err(got, ref[lo:lo + s]) < TOL32, f"portion at {lo} of {s}"
+        lo += s
+
+
+def test_unequal_requests_in_one_batch_with_reused_pages(cases):
+    """four live requests at most, a pool far smaller than the sum of all requests: finished requests hand their pages (and the
+    pooled entries that live in them) to new ones while others are in the middle of their prompt or decoding"""
+    c = cases("mixed")
+    V = c.cfg["vocab"]
+    seqs = {n: toks(L, V, 20 + i) for i, (n, L) in enumerate([("a", 70), ("b", 9), ("c", 31), ("d", 2), ("e", 48), ("f", 17), ("g", 1), ("h", 26)])}
+    eng = c.engine(max_tokens=176, max_seqs=4)
+    plan = [[("a", 30), ("b", 2), ("c", 1)], [("c", 5), ("a", 1), ("b", 7), ("d", 2)], [("a", 25), ("e", 3), ("c", 25)], [("e", 45), ("a", 1), ("f", 2)],
+            [("a", 13), ("f", 15), ("g", 1), ("h", 2)], [("h", 1)], [("h", 23)]]
+    fed = {n: 0 for n in seqs}
+    used_pages = {}
+    for step in plan:
+        entries, end = [], []
+        for n, k in step:
+            entries.append({"id": n, "tokens": seqs[n][fed[n]:fed[n] + k], "want": list(range(k))})
+            if fed[n] + k == len(seqs[n]):
+                end.append(n)
+        got = eng.run_entries(entries, [])
+        for n, _ in step:
+            used_pages[n] = list(eng.cache.live[n].blocks)
+        for n in end:
+            eng.release(n)
+        o = 0
+        for n, k in step:
+            assert err(got[o:o + k], c.ref(seqs[n])[fed[n]:fed[n] + k]) < TOL32, f"{n} at {fed[n]}"
+            o += k
+            fed[n] += k
+    assert all(fed[n] == len(s) for n, s in seqs.items())
+    all_pages = [p for v in used_pages.values() for p in v]
+    assert len(all_pages) > len(set(all_pages))                      # pages went through several owners
+    assert eng.cache.pages.free_blocks == eng.cache.pages.num_blocks and eng.cache.slots.free_slots == 4
+
+
+def test_alone_and_in_a_batch_agree(cases):
+    c = cases("wide")
+    V = c.cfg["vocab"]
+    a, b = toks(60, V, 30), toks(21, V, 31)
+    alone = c.engine(max_tokens=64, max_seqs=1)
+    ra = alone.run_entries([{"id": "a", "tokens": a, "want": [59]}], ["a"])
+    both = c.engine(max_tokens=112, max_seqs=2)
+    both.run_entries([{"id": "b", "tokens": b[:20], "want": []}], [])
+    rb = both.run_entries([{"id": "b", "tokens": b[20:], "want": [0]}, {"id": "a", "tokens": a, "want": [59]}], [])
+    assert err(rb[1:2], torch.from_numpy(ra)) < 1e-5
+    assert err(rb[0:1], c.ref(b)[20:21]) < TOL32
+
+
+@pytest.mark.parametrize("what,delta", [("size", 1), ("size", -1), ("pool", 1)])
+def test_window_and_pool_edges_seen_through_the_whole_model(cases, what, delta):
+    """tokens decoded alone where the first key leaves the window and where the first pooled block appears; the same weights with a
+    window (or a block) one position off give logits that differ there by far more than the tolerance, so a mask that is one off
+    cannot pass"""
+    c = cases("wide")
+    t = toks(70, c.cfg["vocab"], 6)
+    ref = c.ref(t)
+    mask = c.cfg["layers"][0]["mixer"]["mask"]
+    size, pool = mask["size"], mask["pool"]
+    eng = c.engine(max_tokens=80, max_seqs=1)
+    eng.run_entries([{"id": "a", "tokens": t[:size - 2], "want": []}], [])
+    rows = []
+    for i in range(size - 2, size + pool + 3):       # around i = size (the first key has just left) and i = size + pool - 1 (block 0 appears)
+        rows.append(eng.run_entries([{"id": "a", "tokens": [t[i]], "want": [0]}], [])[0])
+    assert err(np.stack(rows), ref[size - 2:size + pool + 3]) < TOL32
+    wrong = copy.deepcopy(c.cfg)
+    wrong["layers"][0]["mixer"]["mask"][what] += delta
+    off = O.forward(wrong, c.P, t[:size + pool + 3])
+    assert err(off[size - 2:], ref[size - 2:size + pool + 3]) > 100 * TOL32
+
+
+def test_greedy_generation_through_the_scheduler(cases):
+    from blazr_b200.engine import SamplingParams
+    c = cases("mixed")
+    V = c.cfg["vocab"]
+    prompts = [toks(n, V, 40 + i) for i, n in enumerate([5, 33, 1, 12, 20, 3])]
+    eng = c.engine(max_tokens=224, max_seqs=3, max_step_tokens=40, prefill_chunk=16)
+    outs = eng.generate(prompts, SamplingParams(max_new_tokens=6))
+    for p, o in zip(prompts, outs):
+        seq = list(p)
+        for k in range(6):
+            lg = O.forward(c.cfg, c.P, seq)[-1]
+            top = torch.topk(lg, 2).values
+            if (top[0] - top[1]).item() >= 1e-3 * lg.std().item():      # a near tie may fall either way in 32-bit: follow the engine
+                assert int(lg.argmax()) == o[k], f"token {k} of prompt of {len(p)}"
+            seq.append(o[k])
+    assert eng.cache.pages.free_blocks == eng.cache.pages.num_blocks
+
+
+def test_trace_replay_command(cases, tmp_path):
+    """bin/trace_run as a user starts it: steps on standard input, logits files and 'done' lines out"""
+    import json
+    import os
+    import subprocess
+    c = cases("odd")
+    folder = str(tmp_path / "m")
+    O.write_checkpoint(folder, c.cfg, c.P)
+    t = toks(30, c.cfg["vocab"], 7)
+    steps = [{"step": 0, "entries": [{"id": "x", "tokens": t[:20], "want": [19]}], "end": []},
+             {"step": 1, "entries": [{"id": "x", "tokens": t[20:29], "want": []}, {"id": "y", "tokens": t[:3], "want": [2]}], "end": ["y"]},
+             {"step": 2, "entries": [{"id": "x", "tokens": t[29:], "want": [0]}], "end": ["x"]}]
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = str(tmp_path / "out")
+    r = subprocess.run([os.path.join(root, "bin", "trace_run"), "--model", folder, "--dtype", "float32", "--out", out, "--max-tokens", "64"],
+                       input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [l for l in r.stdout.splitlines() if l.startswith("done")] == ["done 0", "done 1", "done 2"]
+    ref = c.ref(t)
+    V = c.cfg["vocab"]
+    g = [np.fromfile(os.path.join(out, f"{i}.f32"), dtype="<f4").reshape(1, V) for i in range(3)]
+    assert err(g[0], ref[19:20]) < TOL32 and err(g[1], ref[2:3]) < TOL32 and err(g[2], ref[29:30]) < TOL32
+
+
+CONFIGS["long"] = config([att(dim=24, heads=6, kv=2, size=50, pool=8, rot=24, base=3000.0, scale=0.2, mlp=moe(experts=12, top=3, ff=40, groups=(3, 2), shared=24)),
+                          att(dim=16, heads=4, kv=4, size=130, pool=16, rot=8, scale=0.25, mlp=dense(56))], vocab=77, width=64)
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", TOL32), ("bfloat16", TOL16)])
+def test_long_portions_next_to_single_tokens(cases, dtype, tol):
+    """portions of hundreds of tokens (query tiles over pooled and window key tiles, experts over sorted pairs) in the same steps as
+    single tokens of another request; then both decode side by side"""
+    c = cases("long", dtype)
+    a, b = toks(420, c.cfg["vocab"], 20), toks(160, c.cfg["vocab"], 21)
+    ra, rb = c.ref(a), c.ref(b)
+    eng = c.engine(max_tokens=592, max_seqs=2)
+    all_got, all_ref = [], []
+    if dtype == "bfloat16":        # collect every row, judge the bulk at the end
+        def err(g, r):
+            all_got.append(torch.as_tensor(g)), all_ref.append(r)
+            return 0.0
+    else:
+        err = globals()["err"]
+    got = eng.run_entries([{"id": "b", "tokens": b[:3], "want": [2]}], [])
+    assert err(got, rb[2:3]) < tol
+    got = eng.run_entries([{"id": "a", "tokens": a[:300], "want": [0, 49, 50, 57, 58, 129, 130, 145, 146, 299]}, {"id": "b", "tokens": [b[3]], "want": [0]}], [])
+    assert err(got, torch.cat([ra[[0, 49, 50, 57, 58, 129, 130, 145, 146, 299]], rb[3:4]])) < tol
+    got = eng.run_entries([{"id": "b", "tokens": b[4:135], "want": [0, 130]}, {"id": "a", "tokens": a[300:370], "want": [0, 1, 69]}], [])
+    assert err(got, torch.cat([rb[[4, 134]], ra[[300, 301, 369]]])) < tol
+    for i in range(25):
+        got = eng.run_entries([{"id": "a", "tokens": [a[370 + i]], "want": [0]}, {"id": "b", "tokens": [b[135 + i]], "want": [0]}], [])
+        assert err(got, torch.cat([ra[370 + i:371 + i], rb[135 + i:136 + i]])) < tol, f"decoded token {i}"
+    got = eng.run_entries([{"id": "a", "tokens": a[395:420], "want": [24]}], ["a", "b"])
+    assert err(got, ra[419:420]) < tol
+    if all_got:
+        assert err16(torch.cat(all_got), torch.cat(all_ref)) < tol
+    from blazr_b200 import seqops
+    assert seqops.error_flags() == 0
