@@ -99,6 +99,8 @@ struct TcParams {
     int M, N, K, epi, out_dtype;
     ActParams act;
     int* err;
+    const int32_t* offs;   // grouped form: [E + 1] first row of every group; rows of group e use the weight rows e * N .. e * N + N - 1
+    int E;
 };
 constexpr int EPI_NONE = 0, EPI_GATED = 1, EPI_PLAIN_ACT = 2;
 
@@ -111,7 +113,27 @@ __global__ void __launch_bounds__(128) linear_tc_kernel(const __grid_constant__ 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // token tiles vary fastest: the CTAs that run together share a few weight tiles and all activation tiles, which L2 holds, so the
     // weights cross HBM once instead of once per token tile
-    const int n0 = blockIdx.y * BN, m0 = blockIdx.x * BM;
+    const int n0 = blockIdx.y * BN;
+    int m0 = blockIdx.x * BM, m_end = p.M, wrow0 = n0;
+    if (p.offs) {   // grouped: blockIdx.x counts the row tiles of all groups in group order; a tile never crosses into the next group's rows
+        __shared__ int grp[3];
+        if (threadIdx.x == 0) {
+            int acc = 0, e = 0;
+            grp[2] = -1;
+            for (; e < p.E; ++e) {
+                const int b = p.offs[e], c = p.offs[e + 1] - b;
+                const int nt = (c + BM - 1) / BM;
+                if ((int)blockIdx.x < acc + nt) {
+                    grp[0] = b + ((int)blockIdx.x - acc) * BM, grp[1] = b + c, grp[2] = e;
+                    break;
+                }
+                acc += nt;
+            }
+        }
+        __syncthreads();
+        if (grp[2] < 0) return;   // more tiles were launched than the groups have (the bound does not know the group sizes)
+        m0 = grp[0], m_end = grp[1], wrow0 = grp[2] * p.N + n0;
+    }
     const int nk = (p.K + BK - 1) / BK;
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) mbar_init(&full[s], 1), mbar_init(&empty[s], 1);
@@ -136,7 +158,7 @@ __global__ void __launch_bounds__(128) linear_tc_kernel(const __grid_constant__ 
             if (kb >= STAGES && !mbar_wait_bounded(&empty[s], ((kb / STAGES) - 1) & 1, ab)) break;
             mbar_expect_tx(&full[s], STAGE_BYTES);
             uint8_t* st = smem + (size_t)s * STAGE_BYTES;
-            tma_load_2d(st, &map_w, kb * BK, n0, &full[s]);
+            tma_load_2d(st, &map_w, kb * BK, wrow0, &full[s]);
             tma_load_2d(st + BN * BK * 2, &map_x, kb * BK, m0, &full[s]);
         }
         if (*ab) {   // leave only when the copies already issued have landed (or the bounded wait gives up on them too)
@@ -168,7 +190,7 @@ __global__ void __launch_bounds__(128) linear_tc_kernel(const __grid_constant__ 
         const int n = n0 + warp * 32 + lane;
 #pragma unroll 1
         for (int c = 0; c < BM; c += 16) {
-            if (m0 + c >= p.M) break;            // uniform across the CTA
+            if (m0 + c >= m_end) break;          // uniform across the CTA
             uint32_t r[16];
             tc_ld16(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)c, r);
             tc_wait_ld();
@@ -176,20 +198,20 @@ __global__ void __launch_bounds__(128) linear_tc_kernel(const __grid_constant__ 
                 if (n < p.N) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j)
-                        if (m0 + c + j < p.M) p.y[(int64_t)(m0 + c + j) * p.ldy + n] = __uint_as_float(r[j]);
+                        if (m0 + c + j < m_end) p.y[(int64_t)(m0 + c + j) * p.ldy + n] = __uint_as_float(r[j]);
                 }
             } else if (p.epi == EPI_PLAIN_ACT) {
                 if (n < p.N) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j)
-                        if (m0 + c + j < p.M) store_act(p.act_out, p.out_dtype, (int64_t)(m0 + c + j) * p.ldo + n, act_plain(p.act.kind, __uint_as_float(r[j])));
+                        if (m0 + c + j < m_end) store_act(p.act_out, p.out_dtype, (int64_t)(m0 + c + j) * p.ldo + n, act_plain(p.act.kind, __uint_as_float(r[j])));
                 }
             } else {
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
                     const float mine = __uint_as_float(r[j]);
                     const float other = __shfl_xor_sync(0xffffffffu, mine, 1);
-                    if ((lane & 1) == 0 && n + 1 < p.N && m0 + c + j < p.M)
+                    if ((lane & 1) == 0 && n + 1 < p.N && m0 + c + j < m_end)
                         store_act(p.act_out, p.out_dtype, (int64_t)(m0 + c + j) * p.ldo + (n >> 1), act_gated(p.act, mine, other));
                 }
             }
@@ -228,7 +250,8 @@ bool make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t K, int64
 
 int launch(const void* x, int64_t ldx, const void* w, TcParams p, cudaStream_t st) {
     CUtensorMap mw, mx;
-    if (!make_map(&mw, w, p.N, p.K, p.K) || !make_map(&mx, x, p.M, p.K, ldx)) return fail(B200SEQ_ERR_CUDA, "linear: tensor map encoding failed");
+    const int64_t wrows = p.offs ? (int64_t)p.E * p.N : p.N;
+    if (!make_map(&mw, w, wrows, p.K, p.K) || !make_map(&mx, x, p.M, p.K, ldx)) return fail(B200SEQ_ERR_CUDA, "linear: tensor map encoding failed");
     static bool attr_set = false;
     const int smem = STAGES * STAGE_BYTES + 1024;
     if (!attr_set) {
@@ -237,7 +260,7 @@ int launch(const void* x, int64_t ldx, const void* w, TcParams p, cudaStream_t s
         attr_set = true;
     }
     p.err = error_flag_dev();
-    dim3 grid((p.M + BM - 1) / BM, (p.N + BN - 1) / BN);
+    dim3 grid((p.M + BM - 1) / BM + (p.offs ? p.E : 0), (p.N + BN - 1) / BN);
     linear_tc_kernel<<<grid, 128, smem, st>>>(mw, mx, p);
     SEQ_LAUNCH_CHECK("linear tc");
     return 0;
@@ -254,6 +277,16 @@ bool linear_tc_usable(int x_dtype, int64_t ldx, int M, int N, int K, const void*
 int launch_linear_tc(const void* x, int64_t ldx, const void* w, int M, int N, int K, float* y, int64_t ldy, cudaStream_t st) {
     TcParams p{};
     p.y = y, p.ldy = ldy, p.M = M, p.N = N, p.K = K, p.epi = EPI_NONE;
+    return launch(x, ldx, w, p, st);
+}
+
+// grouped form: rows [offs[e], offs[e + 1]) of x go through the weight w[e] ([E][N][K]); act_kind < 0: f32 product to out, else a plain activation
+int launch_linear_tc_grouped(const void* x, int64_t ldx, const void* w, const int32_t* offs, int E, int rows, int N, int K, int act_kind, void* out, int out_dtype,
+                             int64_t ldo, cudaStream_t st) {
+    TcParams p{};
+    p.M = rows, p.N = N, p.K = K, p.offs = offs, p.E = E;
+    if (act_kind < 0) p.y = reinterpret_cast<float*>(out), p.ldy = ldo, p.epi = EPI_NONE;
+    else p.act_out = out, p.ldo = ldo, p.out_dtype = out_dtype, p.epi = EPI_PLAIN_ACT, p.act = ActParams{act_kind, 0.f, 0.f, 0.f};
     return launch(x, ldx, w, p, st);
 }
 

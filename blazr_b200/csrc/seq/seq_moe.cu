@@ -2,8 +2,9 @@
 //   route   : sigmoid scores, group-limited choice of the `top` experts per token, weights normalised over the chosen ones (all f32).
 //   sort    : (token, choice) pairs ordered by expert, stable, so that one expert's rows form tiles.
 //   linear  : one projection of every pair through its expert's weight.  Few pairs (decode): one launch row per pair, the expert's
-//             weight rows streamed by warps with 16-byte loads.  Many pairs: 64 x 64 f32 fma tiles over each expert's sorted rows
-//             (exact 32-bit arithmetic; rows are gathered through the sort on load).
+//             weight rows streamed by warps with 16-byte loads.  Many pairs: tiles over each expert's sorted rows -- tcgen05 tiles
+//             (the grouped form of seq_linear_tc.cu) for bfloat16 rows that lie in sorted order (gather puts the tokens' rows there),
+//             64 x 64 f32 fma tiles otherwise (exact 32-bit arithmetic; rows are gathered through the sort on load).
 //   combine : weighted sum of a token's expert outputs in choice order, plus an optional shared branch times a sigmoid token gate.
 // A pair's result depends on its token and expert only; which other tokens are in the step changes at most the kernel variant.
 #include "seq_common.cuh"
@@ -11,6 +12,23 @@
 namespace b200seq {
 
 constexpr int MOE_MAX_E = 1024;
+
+bool linear_tc_usable(int x_dtype, int64_t ldx, int M, int N, int K, const void* x, const void* w);
+int launch_linear_tc_grouped(const void* x, int64_t ldx, const void* w, const int32_t* offs, int E, int rows, int N, int K, int act_kind, void* out, int out_dtype,
+                             int64_t ldo, cudaStream_t st);
+
+// grid (pairs): row r of the result = the activation row of the token behind the r-th sorted pair (contiguous rows for the tensor-core tiles)
+__global__ void moe_gather_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, const int32_t* __restrict__ sorted, int x_div, int K,
+                                  __nv_bfloat16* __restrict__ out, int64_t ldo) {
+    const int r = blockIdx.x;
+    const __nv_bfloat16* src = x + (int64_t)(sorted[r] / x_div) * ldx;
+    __nv_bfloat16* dst = out + (int64_t)r * ldo;
+    if ((K & 7) == 0 && (ldx & 7) == 0 && (ldo & 7) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+        for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) *reinterpret_cast<uint4*>(dst + k) = *reinterpret_cast<const uint4*>(src + k);
+    } else {
+        for (int k = threadIdx.x; k < K; k += blockDim.x) dst[k] = src[k];
+    }
+}
 
 // grid (T), one warp per token
 __global__ void moe_route_kernel(const float* __restrict__ z, int64_t ldz, int E, int groups, int keep, int top, int32_t* __restrict__ ids,
@@ -335,12 +353,22 @@ int b200seq_moe_linear(const void* x, int x_dtype, int64_t ldx_, int x_div, cons
         SEQ_LAUNCH_CHECK("moe_linear rows");
         return 0;
     }
+    if (x_div == 0 && pairs >= 32 && linear_tc_usable(x_dtype, ldx_, pairs, N, K, x, w))   // rows laid out like the result: tcgen05 tiles per expert
+        return launch_linear_tc_grouped(x, ldx_, w, offs, E, pairs, N, K, act, out, out_dtype, ldo, cs);
     const int tiles = (pairs + MT - 1) / MT + E;
     if (tiles > 65535) return fail(B200SEQ_ERR_UNSUPPORTED, "moe_linear: too many row tiles");
     dim3 grid((N + MT - 1) / MT, tiles);
     if (x_dtype == B200SEQ_F32) moe_tiled_kernel<float><<<grid, 256, 0, cs>>>(a);
     else moe_tiled_kernel<__nv_bfloat16><<<grid, 256, 0, cs>>>(a);
     SEQ_LAUNCH_CHECK("moe_linear tiles");
+    return 0;
+}
+
+int b200seq_moe_gather(const void* x_bf16, int64_t ldx_, const int32_t* sorted, int x_div, int pairs, int K, void* out_bf16, int64_t ldo, void* stream) {
+    if (!x_bf16 || !sorted || !out_bf16 || x_div < 1 || pairs < 0 || K < 1 || ldx_ < K || ldo < K) return fail(B200SEQ_ERR_INVALID_ARG, "moe_gather: bad arguments");
+    if (pairs == 0) return 0;
+    moe_gather_kernel<<<pairs, K >= 2048 ? 256 : 128, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x_bf16, ldx_, sorted, x_div, K, (__nv_bfloat16*)out_bf16, ldo);
+    SEQ_LAUNCH_CHECK("moe_gather");
     return 0;
 }
 

@@ -168,6 +168,7 @@ class _Workspace:
             self.moe_act = torch.empty((cap * top, F), **act)
             self.moe_ys = torch.empty((cap * top, W), **f32)
             self.moe_sh = torch.empty((cap, W), **f32)
+            self.moe_xs = torch.empty((cap * top, W), **act) if model.act_dtype == torch.bfloat16 else None   # tokens' rows in sorted pair order
         self.scratch = torch.empty(max(1, model.scratch_floats(cap)), **f32)      # work area: segmented state-space scan, key-split attention
         self.next_ids = torch.empty((cap,), dtype=torch.int32, device=dev)
         # int32 step arrays in one buffer: ids | ent | pos | want | start | slot | pos0 | block_table
@@ -584,7 +585,12 @@ class LayeredModel:
         else:
             order, offs, slot = ws.moe_order, ws.moe_off, ws.moe_slot
             ops.moe_sort(ws.moe_ids, pairs, E, ws.moe_cnt, offs, order, slot)
-        ops.moe_linear(a, top, L["w_eup"], ws.moe_ids, order, offs, pairs, kind, mid)
+        if not rows_form and ws.moe_xs is not None and ops.tc_usable(a, a.shape[1]) and f.ff % 8 == 0:
+            xs = ws.moe_xs[:pairs]                  # tensor-core tiles fetch contiguous rows: put the tokens' rows in sorted order first
+            ops.moe_gather(a, top, order, pairs, xs)
+            ops.moe_linear(xs, 0, L["w_eup"], ws.moe_ids, order, offs, pairs, kind, mid)
+        else:
+            ops.moe_linear(a, top, L["w_eup"], ws.moe_ids, order, offs, pairs, kind, mid)
         ops.moe_linear(mid, 0, L["w_edown"], ws.moe_ids, order, offs, pairs, ops.ACT_NONE, ys)
         sh = None
         if f.shared_ff:

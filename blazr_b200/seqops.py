@@ -34,7 +34,7 @@ _DT = {torch.float32: F32, torch.bfloat16: BF16}
 EXPORTS = ["b200seq_last_error", "b200seq_version", "b200seq_launch_count", "b200seq_error_flags", "b200seq_embed_streams", "b200seq_hc_norm", "b200seq_hc_norm_conv",
            "b200seq_causal_conv", "b200seq_group_rmsnorm", "b200seq_gated_act", "b200seq_linear", "b200seq_linear_gated", "b200seq_attn_prep", "b200seq_attn", "b200seq_attn_scratch_floats",
            "b200seq_ssm_scan", "b200seq_ssm_scratch_floats", "b200seq_argmax", "b200seq_linear_act", "b200seq_act", "b200seq_depth_norm", "b200seq_attn_prep_ex",
-           "b200seq_attn_ex", "b200seq_moe_route", "b200seq_moe_sort", "b200seq_moe_linear", "b200seq_moe_combine"]
+           "b200seq_attn_ex", "b200seq_moe_route", "b200seq_moe_sort", "b200seq_moe_linear", "b200seq_moe_gather", "b200seq_moe_combine"]
 
 
 class SeqError(RuntimeError):
@@ -303,6 +303,15 @@ def moe_linear(x: torch.Tensor, x_div: int, w: torch.Tensor, ids: torch.Tensor, 
     assert w.dtype == torch.bfloat16 and w.is_contiguous() and tuple(w.shape[1:]) == (N, K) and out.shape[0] >= pairs
     _check(lib().b200seq_moe_linear(_p(x), _DT[x.dtype], C.c_int64(ldx), x_div, _p(w), _p(ids), _p(order), _p(offs), pairs, E, N, K, act, _p(out), _DT[out.dtype],
                                     C.c_int64(ldo), _st(x)))
+
+
+@_timed
+def moe_gather(x: torch.Tensor, x_div: int, order: torch.Tensor, pairs: int, out: torch.Tensor):
+    """out[r] = x[order[r] // x_div]: the tokens' bf16 activations in the sorted order of their pairs"""
+    _, K, ldx = _rows2d(x)
+    _, _, ldo = _rows2d(out)
+    assert x.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and out.shape[0] >= pairs and out.shape[1] == K
+    _check(lib().b200seq_moe_gather(_p(x), C.c_int64(ldx), _p(order), x_div, pairs, K, _p(out), C.c_int64(ldo), _st(x)))
 
 
 @_timed

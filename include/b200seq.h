@@ -200,6 +200,9 @@ int b200seq_moe_sort(const int32_t* ids, int pairs, int E, const int32_t* counts
  * result).  act: -1 none (out f32) or a plain activation kind (out in out_dtype).  out [pairs, N], stride ldo. */
 int b200seq_moe_linear(const void* x, int x_dtype, int64_t ldx, int x_div, const void* w_bf16, const int32_t* ids, const int32_t* sorted, const int32_t* offs,
                        int pairs, int E, int N, int K, int act, void* out, int out_dtype, int64_t ldo, void* stream);
+/* out[r] = x[sorted[r] / x_div] for every sorted pair r (bf16 rows of K): the tokens' activations in sorted order, so that the tensor-core
+ * tiles of b200seq_moe_linear (sorted rows, x_div = 0, bf16, K % 8 == 0, 16-byte aligned rows, >= 32 pairs) can fetch them. */
+int b200seq_moe_gather(const void* x_bf16, int64_t ldx, const int32_t* sorted, int x_div, int pairs, int K, void* out_bf16, int64_t ldo, void* stream);
 /* y[t] = sum_j wts[t][j] * ys[slot_of ? slot_of[t * top + j] : t * top + j] (j ascending) + (shared ? sigmoid(gate_z[t * ldg]) * shared[t] : 0)
  * gate_z null with shared: the shared branch is added as it is.  ys, shared, y: f32 [., W]. */
 int b200seq_moe_combine(const float* ys, const float* wts, const int32_t* slot_of, int T, int top, int W, const float* shared, const float* gate_z, int64_t ldg,

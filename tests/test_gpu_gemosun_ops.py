@@ -250,7 +250,7 @@ def test_router_choice_and_weights(ops, T, E, top, groups, keep):
 
 
 @pytest.mark.parametrize("T,E,top,N,K,xdt", [(3, 4, 2, 24, 40, torch.float32), (70, 8, 3, 50, 36, torch.float32), (5, 6, 1, 33, 64, torch.bfloat16),
-                                             (130, 5, 2, 72, 96, torch.bfloat16)])
+                                             (130, 5, 2, 72, 96, torch.bfloat16), (600, 9, 3, 200, 136, torch.bfloat16)])
 def test_expert_projections_per_pair_and_over_sorted_tiles(ops, T, E, top, N, K, xdt):
     """up (gathers the token's row, squared relu) and down (plain) in both forms give what each pair's expert gives alone; the combine
     step weighs them in choice order and adds the gated shared branch"""
@@ -279,6 +279,15 @@ def test_expert_projections_per_pair_and_over_sorted_tiles(ops, T, E, top, N, K,
         ops.moe_linear(x.to(DEV), top, w_up.to(DEV), ids_d, order, offs, pairs, ops.ACT_RELU2, mid)
         perm = order.cpu().long() if order is not None else torch.arange(pairs)
         close(mid.float(), mid_ref[perm], 5e-6 if xdt == torch.float32 else 6e-3)
+        if form == "tiles" and xdt == torch.bfloat16 and pairs >= 32:
+            # the tokens' rows gathered into sorted order first: the same projection on tensor-core tiles, one group of rows per expert
+            xs = torch.full((pairs, K), 7.0, device=DEV, dtype=xdt)
+            ops.moe_gather(x.to(DEV), top, order, pairs, xs)
+            assert torch.equal(xs.cpu(), x[perm // top])
+            mid_tc = torch.full((pairs + 1, N), 7.0, device=DEV, dtype=xdt)
+            ops.moe_linear(xs, 0, w_up.to(DEV), ids_d, order, offs, pairs, ops.ACT_RELU2, mid_tc[:pairs])
+            close(mid_tc[:pairs].float(), mid_ref[perm], 6e-3)
+            assert bool((mid_tc[pairs:] == 7.0).all()) and ops.error_flags() == 0
         ys = torch.full((pairs, K), 7.0, device=DEV)
         ops.moe_linear(mid, 0, w_down.to(DEV), ids_d, order, offs, pairs, ops.ACT_NONE, ys)
         ys_ref = torch.stack([mid.float().cpu().double()[r] @ w_down[idf[perm[r]]].double().T for r in range(pairs)])
