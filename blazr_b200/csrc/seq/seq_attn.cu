@@ -29,9 +29,34 @@ __device__ __forceinline__ int64_t pooled_row(const int32_t* bt, int bs, int P, 
     return (int64_t)bt[pg] * ppp + (b - first);
 }
 
-// grid (T), one warp per head unit: H query heads, G key heads, G value heads
+// mean key and mean value of block b (positions b * P .. b * P + P - 1) from the pool's rows, summed in position order
+// (columns c0, c0 + cstep, ... of the G * D key columns followed by the G * V value columns)
+__device__ __forceinline__ void pool_block(const b200seq_step& st, const int32_t* bt, int b, int G, int D, int V, int P, int ppp, const float* __restrict__ kpool,
+                                           const float* __restrict__ vpool, float* __restrict__ kpp, float* __restrict__ vpp, int c0, int cstep) {
+    const int bs = st.block_size;
+    const int64_t prow = pooled_row(bt, bs, P, ppp, b);
+    const int nk = G * D, nv = G * V;
+    const float inv = 1.0f / (float)P;
+    for (int c = c0; c < nk + nv; c += cstep) {
+        const bool isk = c < nk;
+        const float* src = isk ? kpool : vpool;
+        const int cc = isk ? c : c - nk, wdt = isk ? nk : nv;
+        float acc = 0.f;
+#pragma unroll 4
+        for (int j = 0; j < P; ++j) {   // the loads do not depend on one another; the sum keeps position order
+            const int pj = b * P + j;
+            acc += src[((int64_t)bt[pj / bs] * bs + pj % bs) * wdt + cc];
+        }
+        (isk ? kpp : vpp)[prow * wdt + cc] = acc * inv;
+    }
+}
+
+// grid (T), one warp per head unit: H query heads, G key heads, G value heads.  Dynamic shared memory: rot_dims floats, the (cos, sin)
+// of every pair at this token's position, computed once for all heads.  fuse_pool (steps in which every entry brings one token): the
+// block that stores the last position of a pooled block also writes the block's mean -- the other rows are in the pool already.
 __global__ void attn_prep_kernel(float* __restrict__ proj, int64_t ld, b200seq_step st, const b200seq_attn_desc a, float* __restrict__ kpool,
-                                 float* __restrict__ vpool, int* err) {
+                                 float* __restrict__ vpool, float* __restrict__ kpp, float* __restrict__ vpp, int fuse_pool, int* err) {
+    extern __shared__ float rot_sm[];
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
     const int e = st.tok_ent[t];
@@ -39,6 +64,14 @@ __global__ void attn_prep_kernel(float* __restrict__ proj, int64_t ld, b200seq_s
     const int64_t row = kv_row(st, e, pos, err);
     float* base = proj + (int64_t)t * ld;
     const int H = a.H, G = a.G, D = a.D, V = a.V;
+    if (a.rot_dims > 0) {
+        for (int i = threadIdx.x; i < (a.rot_dims >> 1); i += blockDim.x) {
+            float sn, cs;
+            sincosf((float)pos * a.rot_freq[i], &sn, &cs);
+            rot_sm[2 * i] = cs * a.rot_scale, rot_sm[2 * i + 1] = sn * a.rot_scale;
+        }
+        __syncthreads();
+    }
     for (int u = wid; u < H + 2 * G; u += nw) {
         if (u < H + G) {   // q or k head: normalise, rotate
             float* p = u < H ? base + a.q_col + (int64_t)u * D : base + a.k_col + (int64_t)(u - H) * D;
@@ -57,9 +90,7 @@ __global__ void attn_prep_kernel(float* __restrict__ proj, int64_t ld, b200seq_s
                     v = p[d] * rinv;
                     if (d < a.rot_dims) {
                         const float other = p[d ^ 1] * rinv;
-                        float sn, cs;
-                        sincosf((float)pos * a.rot_freq[d >> 1], &sn, &cs);
-                        sn *= a.rot_scale, cs *= a.rot_scale;
+                        const float cs = rot_sm[d & ~1], sn = rot_sm[d | 1];
                         v = (d & 1) ? fmaf(v, cs, other * sn) : fmaf(v, cs, -other * sn);
                     }
                 }
@@ -73,36 +104,26 @@ __global__ void attn_prep_kernel(float* __restrict__ proj, int64_t ld, b200seq_s
             for (int d = lane; d < V; d += 32) dst[d] = p[d];
         }
     }
+    if (fuse_pool && a.pool > 0 && row >= 0 && (pos + 1) % a.pool == 0) {
+        __syncthreads();   // this block's own k and v rows are in the pool
+        const int ppp = (st.block_size + a.pool - 1) / a.pool;
+        pool_block(st, st.block_table + (int64_t)e * st.max_blocks, pos / a.pool, G, D, V, a.pool, ppp, kpool, vpool, kpp, vpp, threadIdx.x, blockDim.x);
+    }
 }
 
-// grid (T): the token that completes a block of P positions writes the block's mean key and mean value
+// grid (T, column slices): the token that completes a block of P positions writes the block's mean key and mean value, one column per thread
 __global__ void attn_pool_kernel(b200seq_step st, int G, int D, int V, int P, int ppp, const float* __restrict__ kpool, const float* __restrict__ vpool,
                                  float* __restrict__ kpp, float* __restrict__ vpp, int* err) {
     const int t = blockIdx.x;
     const int pos = st.tok_pos[t];
     if ((pos + 1) % P != 0) return;
     const int e = st.tok_ent[t];
-    const int bs = st.block_size;
-    if (pos / bs >= st.max_blocks || pos < 0) {
+    if (pos / st.block_size >= st.max_blocks || pos < 0) {
         if (threadIdx.x == 0) atomicOr(err, 1);
         return;
     }
-    const int32_t* bt = st.block_table + (int64_t)e * st.max_blocks;
-    const int b = pos / P;
-    const int64_t prow = pooled_row(bt, bs, P, ppp, b);
-    const int nk = G * D, nv = G * V;
-    const float inv = 1.0f / (float)P;
-    for (int c = threadIdx.x; c < nk + nv; c += blockDim.x) {
-        const bool isk = c < nk;
-        const float* src = isk ? kpool : vpool;
-        const int cc = isk ? c : c - nk, wdt = isk ? nk : nv;
-        float acc = 0.f;
-        for (int j = 0; j < P; ++j) {
-            const int pj = b * P + j;
-            acc += src[((int64_t)bt[pj / bs] * bs + pj % bs) * wdt + cc];
-        }
-        (isk ? kpp : vpp)[prow * wdt + cc] = acc * inv;
-    }
+    pool_block(st, st.block_table + (int64_t)e * st.max_blocks, pos / P, G, D, V, P, ppp, kpool, vpool, kpp, vpp, blockIdx.y * blockDim.x + threadIdx.x,
+               gridDim.y * blockDim.x);
 }
 
 // ---- attend -----------------------------------------------------------------------------------------------------------------------
@@ -421,11 +442,14 @@ int b200seq_attn_prep_ex(float* proj, int64_t ld, const b200seq_step* st, const 
     if (int rc = desc_check(d, "attn_prep")) return rc;
     if (d->pool > 0 && (!kpooled || !vpooled)) return fail(B200SEQ_ERR_INVALID_ARG, "attn_prep: pooled blocks need their pools");
     if (st->T == 0) return 0;
-    attn_prep_kernel<<<st->T, 256, 0, (cudaStream_t)stream>>>(proj, ld, *st, *d, kpool, vpool, error_flag_dev());
+    const int fuse_pool = d->pool > 0 && st->T == st->B;   // one token per entry: no other block of this step writes a row the mean reads
+    attn_prep_kernel<<<st->T, 256, (size_t)d->rot_dims * sizeof(float), (cudaStream_t)stream>>>(proj, ld, *st, *d, kpool, vpool, kpooled, vpooled, fuse_pool,
+                                                                                                 error_flag_dev());
     SEQ_LAUNCH_CHECK("attn_prep");
-    if (d->pool > 0) {
+    if (d->pool > 0 && !fuse_pool) {
         const int ppp = (st->block_size + d->pool - 1) / d->pool;
-        attn_pool_kernel<<<st->T, 128, 0, (cudaStream_t)stream>>>(*st, d->G, d->D, d->V, d->pool, ppp, kpool, vpool, kpooled, vpooled, error_flag_dev());
+        const int cols = d->G * (d->D + d->V);
+        attn_pool_kernel<<<dim3(st->T, (cols + 255) / 256), 256, 0, (cudaStream_t)stream>>>(*st, d->G, d->D, d->V, d->pool, ppp, kpool, vpool, kpooled, vpooled, error_flag_dev());
         SEQ_LAUNCH_CHECK("attn_pool");
     }
     return 0;

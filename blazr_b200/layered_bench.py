@@ -6,8 +6,9 @@ dense-attention decoder (blazr_b200/decode.py, Q8_0 weights) of the same width, 
     kernels  : every operator of one prefill step and one decode step timed alone (CUDA events around each launch), with its
                algorithmic bytes / FLOPs and the fraction of the roofline it reaches; the like kernels of the decoder beside them
 
-`python bench.py --layered fenorax [--layered-sizes w1024,w2048]` prints the result as one JSON line; bench.py's default workload
-and JSON line are untouched.
+`python bench.py --layered fenorax|gemosun [--layered-sizes w1024,w2048]` prints the result as one JSON line; bench.py's default
+workload and JSON line are untouched.  For Gemosun (parallel attention / feed-forward layers, three of four feed-forwards a mixture of
+experts) the closest existing model, Fenorax at the same sizes, runs beside it as well.
 """
 from __future__ import annotations
 
@@ -38,6 +39,51 @@ def fenorax_config(sz: dict, streams: int = 2, taps: int = 3) -> dict:
            "mixer": {"dim": sz["dim"], "vdim": sz["dim"], "heads": sz["heads"], "kv_heads": sz["kv_heads"], "scale": sz["dim"] ** -0.5, "mask": {"size": sz["chunk"]}}}
     return {"architecture": "Fenorax", "vocab": sz["vocab"], "width": sz["width"], "streams": streams, "norm": {"eps": 1e-5, "groups": 2}, "canon": {"taps": taps},
             "embedding": {"scale": float(sz["width"]) ** 0.5}, "layers": [ssm, att, ssm, att]}
+
+
+def gemosun_config(sz: dict, experts: int = 32, top: int = 4) -> dict:
+    """four parallel layers of the size's width and head layout: sliding window of `chunk` positions with pooled blocks of 16, rotation of
+    half of every head with scaled frequencies; feed-forwards [dense, experts, experts, experts], an expert a quarter of the dense size"""
+    def att(mlp):
+        return {"type": "attention", "mlp": mlp,
+                "mixer": {"dim": sz["dim"], "vdim": sz["dim"], "heads": sz["heads"], "kv_heads": sz["kv_heads"], "scale": sz["dim"] ** -0.5,
+                          "mask": {"size": sz["chunk"], "pool": 16},
+                          "rot": {"dims": sz["dim"] // 2, "base": 10000.0, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}}
+    eff = sz["ff"] // 4
+    moe = {"kind": "moe", "expert": {"ff": eff}, "router": {"experts": experts, "top": top, "groups": {"count": 4, "keep": 2}}, "shared": {"ff": eff}}
+    return {"architecture": "Gemosun", "vocab": sz["vocab"], "width": sz["width"], "norm": {"eps": 1e-5},
+            "layers": [att({"kind": "dense", "ff": sz["ff"]}), att(dict(moe)), att(dict(moe)), att(dict(moe))]}
+
+
+def random_tensors_gemosun(cfg: dict, device, seed: int = 7):
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    W = cfg["width"]
+
+    def rnd(*shape, scale=1.0):
+        return (torch.randn(shape, generator=g, device=device) * scale).to(torch.bfloat16)
+
+    ones = lambda n: torch.ones(n, dtype=torch.bfloat16, device=device)
+    t = {"embed": rnd(cfg["vocab"], W), "head": rnd(cfg["vocab"], W, scale=W ** -0.5), "final.norm": ones(W)}
+    for i, lay in enumerate(cfg["layers"]):
+        p, m, mlp = f"l{i}.", lay["mixer"], lay["mlp"]
+        H, G, D = m["heads"], m["kv_heads"], m["dim"]
+        t[p + "norm1"], t[p + "norm2"] = ones(W), ones(W)
+        t[p + "mix.q"], t[p + "mix.k"] = rnd(H * D, W, scale=W ** -0.5), rnd(G * D, W, scale=W ** -0.5)
+        t[p + "mix.g"], t[p + "mix.o"] = rnd(H, W, scale=W ** -0.5), rnd(W, H * D, scale=(H * D) ** -0.5)
+        if mlp["kind"] == "dense":
+            ff = mlp["ff"]
+            t[p + "mlp.gate"], t[p + "mlp.up"], t[p + "mlp.down"] = rnd(ff, W, scale=W ** -0.5), rnd(ff, W, scale=W ** -0.5), rnd(W, ff, scale=ff ** -0.5)
+        else:
+            E, ff, sf = mlp["router"]["experts"], mlp["expert"]["ff"], mlp["shared"]["ff"]
+            t[p + "mlp.router"] = rnd(E, W, scale=2.0 * W ** -0.5)
+            for e in range(E):
+                t[p + f"mlp.e{e}.up"], t[p + f"mlp.e{e}.down"] = rnd(ff, W, scale=W ** -0.5), rnd(W, ff, scale=ff ** -0.5)
+            t[p + "mlp.shared.up"], t[p + "mlp.shared.down"], t[p + "mlp.shared.sg"] = rnd(sf, W, scale=W ** -0.5), rnd(W, sf, scale=sf ** -0.5), rnd(1, W, scale=W ** -0.5)
+        d = torch.full((i + 2,), 0.1 / (i + 1), device=device)
+        d[i + 1] = 0.9
+        t[p + "dwa"] = d.to(torch.bfloat16)
+    return t.__getitem__
 
 
 def random_tensors(cfg: dict, device, seed: int = 7):
@@ -83,19 +129,50 @@ def _events():
 
 
 def _linear_weights(model: LayeredModel) -> int:
-    return sum(L[k].numel() for L in model.layers for k in ("w_in", "w_o", "w_gu", "w_down") if k in L)
+    """weights of the linear layers a token goes through (of a mixture of experts: the router, the chosen experts, the shared one)"""
+    n = sum(L[k].numel() for L in model.layers for k in ("w_in", "w_o", "w_gu", "w_down", "w_router", "w_sup", "w_sdown") if k in L)
+    for L in model.layers:
+        if "w_eup" in L:
+            n += L["spec"].ff.top * (L["w_eup"][0].numel() + L["w_edown"][0].numel())
+    return n
 
 
 # ---- cost model: algorithmic bytes and FLOPs of one operator call, from the shapes the timeline recorded ---------------------------
-def _cost(name: str, shapes, scal, scen: dict):
+def _cost(name: str, shapes, scal, scen: dict, kw: dict = None):
+    kw = kw or {}
     sh = [s for s in shapes if s is not None]
     by = lambda s: int(np.prod(s[0])) * s[1]
-    if name in ("linear", "linear_gated"):
+    if name == "depth_norm":      # x_cur, out1, w1 positional; the branches, the earlier results and the outputs by keyword
+        rows = kw["rows"][0][0] if isinstance(kw.get("rows"), tuple) else sh[0][0][0]
+        W = sh[0][0][1]
+        reads = 1 + sum(1 for n in ("y1", "y2") if isinstance(kw.get(n), tuple)) + (kw.get("n_prev", 0) if isinstance(kw.get("dwa"), tuple) else 0)
+        writes = sum(1 for n in ("hist_out", "x_out") if isinstance(kw.get(n), tuple)) if isinstance(kw.get("y1"), tuple) else 0
+        outs = sum(s[1] for s in (shapes[1], kw.get("out2")) if isinstance(s, tuple))
+        return rows * W * (4 * (reads + writes) + outs), 0.0, "hbm"
+    if name in ("attn_prep", "attn_prep_ex"):     # the projection row in, q back, k and v rows to the pool (the pools are not streamed)
+        d = scen.get("attn_desc")
+        T, ld = sh[0][0]
+        if name == "attn_prep_ex" and d is not None:
+            return T * (ld + d.H * d.D + d.G * (d.D + d.V)) * 4, 0.0, "hbm"
+        return T * ld * 4 * 2, 0.0, "hbm"
+    if name in ("linear", "linear_gated", "linear_act"):
         (xs, xe), (ws, _), (ys, ye) = sh[0], sh[1], sh[2]
         M, K, N = xs[0], xs[1], ws[0]
         return M * K * xe + N * K * 2 + int(np.prod(ys)) * ye, 2.0 * M * N * K, "tensor"
-    if name == "attn":
-        T, H, G, D, V = sh[0][0][0], scal[0], scal[1], scal[2], scal[3]
+    if name == "moe_linear":      # x, w [E, N, K], ids, (order, offs), out; scal: x_div, pairs, act
+        (xs, xe), (ws, _) = sh[0], sh[1]
+        pairs = scal[1]
+        E, N, K = ws
+        (os_, oe) = sh[-1]
+        rows_in = pairs if scal[0] == 0 else xs[0]
+        w_read = min(E, pairs) * N * K * 2           # every expert that has a pair streams its weight once
+        return rows_in * K * xe + w_read + pairs * N * oe, 2.0 * pairs * N * K, "tensor"
+    if name in ("attn", "attn_ex"):
+        if name == "attn_ex":
+            d = scen["attn_desc"]
+            T, H, G, D, V = sh[0][0][0], d.H, d.G, d.D, d.V
+        else:
+            T, H, G, D, V = sh[0][0][0], scal[0], scal[1], scal[2], scal[3]
         keys = scen["visible_keys"]                              # sum over the step's tokens of the keys each one sees
         kv_once = scen["kv_rows_touched"] * G * (D + V) * 4      # every visible K / V row once
         return kv_once + T * H * (D + V) * 4, 2.0 * keys * H * (D + V), "f32" if scen["prefill"] else "hbm"
@@ -129,12 +206,15 @@ def kernel_table(model: LayeredModel, eng: Engine, run, scen: dict, pk) -> List[
         seqops.timeline = None
         model.use_graphs = graphs
     agg: Dict[str, dict] = {}
-    for name, shapes, scal, e0, e1 in tl:
+    for name, shapes, scal, e0, e1, kw in tl:
         key = name
-        if name in ("linear", "linear_gated"):
+        if name in ("linear", "linear_gated", "linear_act"):
             sh = [s for s in shapes if s is not None]
             key = f"{name} M={sh[0][0][0]} N={sh[1][0][0]} K={sh[0][0][1]}"
-        b, f, kind = _cost(name, shapes, scal, scen)
+        elif name == "moe_linear":
+            sh = [s for s in shapes if s is not None]
+            key = f"moe_linear pairs={scal[1]} E={sh[1][0][0]} N={sh[1][0][1]} K={sh[1][0][2]}"
+        b, f, kind = _cost(name, shapes, scal, scen, kw)
         a = agg.setdefault(key, dict(op=key, calls=0, us=0.0, bytes=0, flops=0.0, roof_us=0.0, bound=kind))
         a["calls"] += 1
         a["us"] += e0.elapsed_time(e1) * 1e3
@@ -153,18 +233,28 @@ def kernel_table(model: LayeredModel, eng: Engine, run, scen: dict, pk) -> List[
 # ---- the design's arm ----------------------------------------------------------------------------------------------------------------
 def bench_layered(design: str, size: str, pk, S: int = 4096, ctx: int = 1024, batches=(1, 4), steps: int = 32, dtype: str = "bfloat16") -> dict:
     from . import registry
-    if design.lower() != "fenorax":
-        raise ValueError(f"no synthetic workload for design '{design}'")
     sz = SIZES[size]
-    cfg = fenorax_config(sz)
     dev = torch.device("cuda", torch.cuda.current_device())
-    model = LayeredModel(registry.LAYERED["Fenorax"](cfg), random_tensors(cfg, dev), dev, dtype)
+    if design.lower() == "fenorax":
+        cfg = fenorax_config(sz)
+        model = LayeredModel(registry.LAYERED["Fenorax"](cfg), random_tensors(cfg, dev), dev, dtype)
+    elif design.lower() == "gemosun":
+        cfg = gemosun_config(sz)
+        model = LayeredModel(registry.LAYERED["Gemosun"](cfg), random_tensors_gemosun(cfg, dev), dev, dtype)
+    else:
+        raise ValueError(f"no synthetic workload for design '{design}'")
+    gem = design.lower() == "gemosun"
+    pool = 16 if gem else 0
+    desc0 = next((L["desc"] for L in model.layers if "desc" in L), None)
     Bmax = max(batches)
     eng = Engine(model, max_tokens=max(S, Bmax * (ctx + steps + 64)) + 64, max_seqs=Bmax, max_step_tokens=max(S, 2048), prefill_chunk=S)
     rng = np.random.default_rng(3)
     prompt = rng.integers(0, sz["vocab"], S).tolist()
-    out = {"size": size, "config": {k: sz[k] for k in sz}, "layers": [l["type"] + ("+ff" if l["mlp"] else "") for l in cfg["layers"]], "streams": cfg["streams"],
-           "linear_weights": _linear_weights(model), "weight_bytes": model.weight_bytes}
+    out = {"size": size, "config": {k: sz[k] for k in sz}, "layers": [l["type"] + ("+" + l["mlp"].get("kind", "ff") if l["mlp"] else "") for l in cfg["layers"]],
+           "streams": cfg.get("streams", 1), "linear_weights": _linear_weights(model), "weight_bytes": model.weight_bytes}
+    if gem:
+        r = cfg["layers"][1]["mlp"]
+        out["experts"] = {"experts": r["router"]["experts"], "top": r["router"]["top"], "ff": r["expert"]["ff"], "shared_ff": r["shared"]["ff"], "groups": r["router"]["groups"]}
     lin_flops_tok = 2.0 * (_linear_weights(model) + 0)
 
     # prefill: whole prompt in one step, logits of the last token, device timed; then through run_entries (host arrays in, logits out)
@@ -194,7 +284,11 @@ def bench_layered(design: str, size: str, pk, S: int = 4096, ctx: int = 1024, ba
                       "linear_TFLOPs": round(lin_flops_tok * S / (ms * 1e-3) / 1e12, 1)}
     chunk = sz["chunk"]
     pos = np.arange(S)
-    scen = dict(prefill=True, entries=1, visible_keys=int((pos - (pos // chunk) * chunk + 1).sum()), kv_rows_touched=S)
+    if gem:     # window of `chunk` positions plus one pooled entry per block of 16 wholly before it
+        vis = np.minimum(pos + 1, chunk) + np.maximum(0, (pos - chunk + 1) // pool)
+        scen = dict(prefill=True, entries=1, visible_keys=int(vis.sum()), kv_rows_touched=S + S // pool, attn_desc=desc0)
+    else:
+        scen = dict(prefill=True, entries=1, visible_keys=int((pos - (pos // chunk) * chunk + 1).sum()), kv_rows_touched=S, attn_desc=desc0)
     out["prefill"]["kernels"] = kernel_table(model, eng, prefill_once, scen, pk)
 
     # decode: B requests of ctx tokens, then one token each per step
@@ -227,11 +321,19 @@ def bench_layered(design: str, size: str, pk, S: int = 4096, ctx: int = 1024, ba
         e1.record()
         torch.cuda.synchronize()
         msd_e2e = e0.elapsed_time(e1) / steps
+        # weights a step streams: all of them but the experts no token of the step chose (at most B * top of a layer's experts are touched)
+        touched = model.weight_bytes
+        for L in model.layers:
+            if "w_eup" in L:
+                E_, per = L["w_eup"].shape[0], (L["w_eup"][0].numel() + L["w_edown"][0].numel()) * 2
+                touched -= (E_ - min(E_, B * L["spec"].ff.top)) * per
         row = {"batch": B, "context": ctx, "ms_per_step": round(msd, 4), "tokens_per_s": round(B / msd * 1e3, 1), "e2e_tokens_per_s": round(B / msd_e2e * 1e3, 1),
-               "weight_GBs": round(model.weight_bytes / (msd * 1e-3) / 1e9, 1), "frac_hbm_weights_only": round(model.weight_bytes / (msd * 1e-3) / 1e9 / pk["hbm_gbs"], 3)}
+               "weight_bytes_touched": touched, "weight_GBs": round(touched / (msd * 1e-3) / 1e9, 1),
+               "frac_hbm_weights_only": round(touched / (msd * 1e-3) / 1e9 / pk["hbm_gbs"], 3)}
         held = eng.cache.live[ids[0]].n_tokens
         lo = (held // chunk) * chunk
-        scen = dict(prefill=False, entries=B, visible_keys=B * (held - lo + 1), kv_rows_touched=B * (held - lo + 1))
+        seen = (min(held + 1, chunk) + max(0, (held - chunk + 1) // pool)) if gem else held - lo + 1
+        scen = dict(prefill=False, entries=B, visible_keys=B * seen, kv_rows_touched=B * seen, attn_desc=desc0)
         row["kernels"] = kernel_table(model, eng, dec_step, scen, pk)
         out["decode"].append(row)
         for r in ids:
@@ -387,6 +489,11 @@ def run(design: str, sizes: List[str], pk, pk_kind: str, S: int = 4096, ctx: int
     for size in sizes:
         row = {"size": size}
         row[design.lower()] = bench_layered(design, size, pk, S=S, ctx=ctx, steps=steps)
+        if design.lower() != "fenorax":     # the closest existing layer-list model at the same sizes
+            try:
+                row["fenorax"] = bench_layered("fenorax", size, pk, S=S, ctx=ctx, steps=steps)
+            except Exception as ex:
+                row["fenorax"] = {"error": repr(ex)[:300]}
         try:
             row["dense_decoder"] = bench_decoder(size, pk, S=S, ctx=ctx, steps=steps)
         except Exception as ex:    # the comparison arm must not take the design's numbers down

@@ -140,7 +140,8 @@ def _rows2d(t: torch.Tensor):
 
 
 # ---- per-operator timeline (bench / profiling aid): set `timeline = []` and every operator call appends
-#      (name, shapes of its tensor arguments, scalar arguments, start event, end event); None (default) costs nothing ----------
+#      (name, shapes of its positional tensor arguments, positional scalars, start event, end event, keyword arguments as shapes /
+#      scalars); None (default) costs nothing ------------------------------------------------------------------------------------
 timeline = None
 
 
@@ -157,7 +158,8 @@ def _timed(fn):
         e1.record()
         shapes = tuple((tuple(t.shape), t.element_size()) if isinstance(t, torch.Tensor) else None for t in a)
         scal = tuple(t for t in a if isinstance(t, (int, float, bool)))
-        tl.append((name, shapes, scal, e0, e1))
+        kw = {n: ((tuple(t.shape), t.element_size()) if isinstance(t, torch.Tensor) else t) for n, t in k.items() if isinstance(t, (torch.Tensor, int, float, bool))}
+        tl.append((name, shapes, scal, e0, e1, kw))
         return r
 
     wrap.__name__, wrap.__doc__ = name, fn.__doc__
