@@ -72,6 +72,8 @@ __global__ void attn_prep_kernel(float* __restrict__ proj, int64_t ld, b200seq_s
         }
         __syncthreads();
     }
+    // 16-byte form: a lane holds two whole pairs, so the rotation needs no neighbour and q turns in place without a barrier
+    const bool vec4 = ((D | V | a.q_col | a.k_col | a.v_col) & 3) == 0 && (ld & 3) == 0 && (reinterpret_cast<uintptr_t>(proj) & 15) == 0;
     for (int u = wid; u < H + 2 * G; u += nw) {
         if (u < H + G) {   // q or k head: normalise, rotate
             float* p = u < H ? base + a.q_col + (int64_t)u * D : base + a.k_col + (int64_t)(u - H) * D;
@@ -83,6 +85,25 @@ __global__ void attn_prep_kernel(float* __restrict__ proj, int64_t ld, b200seq_s
                 rinv = 1.0f / sqrtf(ss / (float)D + a.qk_eps);
             }
             float* dst = u < H ? p : (row >= 0 ? kpool + (row * G + (u - H)) * D : nullptr);
+            if (vec4) {
+                if (dst) {
+                    for (int i = lane; i < (D >> 2); i += 32) {
+                        float4 v = reinterpret_cast<const float4*>(p)[i];
+                        v.x *= rinv, v.y *= rinv, v.z *= rinv, v.w *= rinv;
+                        const int d = 4 * i;
+                        if (d < a.rot_dims) {
+                            const float cs = rot_sm[d], sn = rot_sm[d + 1], x = v.x, y = v.y;
+                            v.x = fmaf(x, cs, -y * sn), v.y = fmaf(y, cs, x * sn);
+                        }
+                        if (d + 2 < a.rot_dims) {
+                            const float cs = rot_sm[d + 2], sn = rot_sm[d + 3], x = v.z, y = v.w;
+                            v.z = fmaf(x, cs, -y * sn), v.w = fmaf(y, cs, x * sn);
+                        }
+                        reinterpret_cast<float4*>(dst)[i] = v;
+                    }
+                }
+                continue;
+            }
             for (int d0 = 0; d0 < D; d0 += 32) {   // a pair (2i, 2i + 1) lies in one pass: both are read before either is written
                 const int d = d0 + lane;
                 float v = 0.f;
@@ -101,7 +122,11 @@ __global__ void attn_prep_kernel(float* __restrict__ proj, int64_t ld, b200seq_s
             const int g = u - H - G;
             const float* p = base + a.v_col + (int64_t)g * V;
             float* dst = vpool + (row * G + g) * V;
-            for (int d = lane; d < V; d += 32) dst[d] = p[d];
+            if (vec4) {
+                for (int i = lane; i < (V >> 2); i += 32) reinterpret_cast<float4*>(dst)[i] = reinterpret_cast<const float4*>(p)[i];
+            } else {
+                for (int d = lane; d < V; d += 32) dst[d] = p[d];
+            }
         }
     }
     if (fuse_pool && a.pool > 0 && row >= 0 && (pos + 1) % a.pool == 0) {
