@@ -154,6 +154,9 @@ class _Workspace:
             self.xbuf = torch.empty((cap, W), **f32)
             self.a2 = torch.empty((cap, W), **act)
             self.y2 = torch.empty((cap, W), **f32)
+            # the feed-forward branch runs beside the mixer on a second stream: it keeps its own intermediates
+            self.ff_inner = torch.empty((cap, max(1, model.max_ff_inner)), **act)
+            self.ff_proj = torch.empty((cap, max(1, model.max_ff_proj)), **f32)
         mo = model.moe_dims
         if mo is not None:              # mixture of experts: router logits, choices, sort, per-pair intermediates
             E1, top, F = mo
@@ -232,6 +235,7 @@ class LayeredModel:
         self.ones_in = torch.ones(S, dtype=torch.float32, device=dev)
         self.layers: List[Dict[str, object]] = []
         self.max_proj = self.max_xbc = self.max_inner = 1
+        self.max_ff_inner = self.max_ff_proj = 1      # depth layout: sizes of the feed-forward branch's own intermediates
         self.moe_dims = None      # (experts + 1, top, expert ff): largest over the layers
         self.weight_bytes = self.embed.numel() * 2 + (0 if cfg.tied_head else self.head.numel() * 2)
         for i, ls in enumerate(cfg.layers):
@@ -302,8 +306,8 @@ class LayeredModel:
                     if tuple(L["w_sup"].shape) != (f.shared_ff, W) or tuple(L["w_sdown"].shape) != (W, f.shared_ff):
                         raise ValueError(f"layer {i}: shared expert tensor shapes do not fit the configuration")
                     self.weight_bytes += (L["w_sup"].numel() + L["w_sdown"].numel()) * 2
-                    self.max_inner = max(self.max_inner, f.shared_ff)
-                    self.max_proj = max(self.max_proj, f.shared_ff)
+                    self.max_ff_inner = max(self.max_ff_inner, f.shared_ff)
+                    self.max_ff_proj = max(self.max_ff_proj, f.shared_ff)
                 md = self.moe_dims or (1, 1, 1)
                 self.moe_dims = (max(md[0], f.experts + 1), max(md[1], f.top), max(md[2], f.ff))
                 if not depth:
@@ -320,14 +324,20 @@ class LayeredModel:
                 L["w_down"] = lin(p + "mlp.down")
                 if tuple(gu.shape) != (2 * ls.ff.ff, W) or tuple(L["w_down"].shape) != (W, ls.ff.ff):
                     raise ValueError(f"layer {i}: feed-forward tensor shapes do not fit the configuration")
-                self.max_proj = max(self.max_proj, 2 * ls.ff.ff)
-                self.max_inner = max(self.max_inner, ls.ff.ff)
+                if depth:
+                    self.max_ff_proj = max(self.max_ff_proj, 2 * ls.ff.ff)
+                    self.max_ff_inner = max(self.max_ff_inner, ls.ff.ff)
+                else:
+                    self.max_proj = max(self.max_proj, 2 * ls.ff.ff)
+                    self.max_inner = max(self.max_inner, ls.ff.ff)
                 self.weight_bytes += (L["w_gu"].numel() + L["w_down"].numel()) * 2
             self.layers.append(L)
         self.max_seqs = self.max_blocks = self.block_size = 0
         self._ws: Dict[int, _Workspace] = {}
         self._graphs: Dict[int, object] = {}
         self.use_graphs = True
+        self.overlap_branches = True     # depth layout: mixer and feed-forward of a layer on two streams
+        self._side = None
 
     # ---- cache and state -------------------------------------------------------------------------------------------------------
     def allocate(self, num_blocks: int, block_size: int, max_seqs: int, max_seq_tokens: int) -> None:
@@ -471,17 +481,37 @@ class LayeredModel:
             L0 = self.layers[0]
             ops.depth_norm(x0, a1, L0["norm1"], cfg.eps, out2=a2 if L0["spec"].ff is not None else None, w2=L0.get("norm2"))
         x_cur = x0
+        # the two branches of a layer read the same input and do not depend on one another: the feed-forward runs on a second stream
+        # beside the mixer (inside a captured decode step they become parallel branches of the graph).  Not while operators are timed alone.
+        two_streams = self.overlap_branches and self.dev.type == "cuda" and seqops.timeline is None
+        if two_streams and self._side is None:
+            self._side = torch.cuda.Stream(self.dev)
         for i, L in enumerate(self.layers):
             ls: LayerSpec = L["spec"]
-            if ls.kind == "attention":
-                self._attention(L, ls.mixer, ws, st, T, a1, y1)
-            else:
+            if ls.kind != "attention":
                 raise ValueError("the depth-averaged layout is wired for attention mixers")
             has_ff = ls.ff is not None
-            if isinstance(ls.ff, MoeFfSpec):
-                self._moe_ff(L, ls.ff, ws, T, a2, y2)
-            elif has_ff:
-                self._dense_ff(L, ls.ff, ws, T, a2, y2)
+
+            def feed_forward():
+                if isinstance(ls.ff, MoeFfSpec):
+                    self._moe_ff(L, ls.ff, ws, T, a2, y2)
+                else:
+                    self._dense_ff(L, ls.ff, ws, T, a2, y2, inner=ws.ff_inner, proj=ws.ff_proj)
+
+            if has_ff and two_streams:
+                main = torch.cuda.current_stream(self.dev)
+                fork, join = torch.cuda.Event(), torch.cuda.Event()
+                fork.record(main)
+                self._side.wait_event(fork)
+                with torch.cuda.stream(self._side):
+                    feed_forward()
+                    join.record(self._side)
+                self._attention(L, ls.mixer, ws, st, T, a1, y1)
+                main.wait_event(join)
+            else:
+                self._attention(L, ls.mixer, ws, st, T, a1, y1)
+                if has_ff:
+                    feed_forward()
             upd = dict(y1=y1, y2=y2 if has_ff else None, hist=hist, n_prev=i + 1, dwa=L["dwa"], x_out=xbuf)
             if i + 1 < n:
                 N = self.layers[i + 1]
@@ -551,18 +581,20 @@ class LayeredModel:
         seqops.group_rmsnorm(yg, L["mnorm"], m.norm_groups, self.cfg.eps, yn)
         seqops.linear(yn, L["w_o"], y)
 
-    def _dense_ff(self, L, f: DenseFfSpec, ws: _Workspace, T: int, a: torch.Tensor, y: torch.Tensor) -> None:
-        act = ws.inner_a.view(-1)[:T * f.ff].view(T, f.ff)
-        self._proj_act(ws, T, a, L["w_gu"], seqops.ACT_KINDS[f.act], act, f.limit, f.alpha, f.up_shift)
+    def _dense_ff(self, L, f: DenseFfSpec, ws: _Workspace, T: int, a: torch.Tensor, y: torch.Tensor, inner: Optional[torch.Tensor] = None,
+                  proj: Optional[torch.Tensor] = None) -> None:
+        inner = ws.inner_a if inner is None else inner
+        act = inner.view(-1)[:T * f.ff].view(T, f.ff)
+        self._proj_act(ws.proj if proj is None else proj, T, a, L["w_gu"], seqops.ACT_KINDS[f.act], act, f.limit, f.alpha, f.up_shift)
         seqops.linear(act, L["w_down"], y)
 
-    def _proj_act(self, ws: _Workspace, T: int, a: torch.Tensor, w: torch.Tensor, kind: int, out: torch.Tensor, limit: float = 0.0, alpha: float = 0.0,
+    def _proj_act(self, proj: torch.Tensor, T: int, a: torch.Tensor, w: torch.Tensor, kind: int, out: torch.Tensor, limit: float = 0.0, alpha: float = 0.0,
                   shift: float = 0.0) -> None:
-        """out = act(a . w^T): projection and activation in one kernel where a fused path takes the step, else product + activation"""
+        """out = act(a . w^T): projection and activation in one kernel where a fused path takes the step, else product (in `proj`) + activation"""
         if T <= 8 or (T >= seqops.TC_MIN_ROWS and seqops.tc_usable(a, a.shape[1])):
             seqops.linear_act(a, w, kind, out, limit, alpha, shift)
         else:
-            z = ws.proj[:T, :w.shape[0]]
+            z = proj[:T, :w.shape[0]]
             seqops.linear(a, w, z)
             seqops.act(z, kind, out, limit, alpha, shift)
 
@@ -594,8 +626,8 @@ class LayeredModel:
         ops.moe_linear(mid, 0, L["w_edown"], ws.moe_ids, order, offs, pairs, ops.ACT_NONE, ys)
         sh = None
         if f.shared_ff:
-            smid = ws.inner_a.view(-1)[:T * f.shared_ff].view(T, f.shared_ff)
-            self._proj_act(ws, T, a, L["w_sup"], kind, smid)
+            smid = ws.ff_inner.view(-1)[:T * f.shared_ff].view(T, f.shared_ff)
+            self._proj_act(ws.ff_proj, T, a, L["w_sup"], kind, smid)
             sh = ws.moe_sh[:T]
             ops.linear(smid, L["w_sdown"], sh)
         ops.moe_combine(ys, ws.moe_wts, slot, T, top, sh, z[:, E] if gated_shared else None, y)

@@ -48,7 +48,7 @@ def gemosun_config(sz: dict, experts: int = 32, top: int = 4) -> dict:
         return {"type": "attention", "mlp": mlp,
                 "mixer": {"dim": sz["dim"], "vdim": sz["dim"], "heads": sz["heads"], "kv_heads": sz["kv_heads"], "scale": sz["dim"] ** -0.5,
                           "mask": {"size": sz["chunk"], "pool": 16},
-                          "rot": {"dims": sz["dim"] // 2, "base": 10000.0, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}}
+                          "rot": {"dims": sz["dim"] // 2, "base": 10000.0, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}}
     eff = sz["ff"] // 4
     moe = {"kind": "moe", "expert": {"ff": eff}, "router": {"experts": experts, "top": top, "groups": {"count": 4, "keep": 2}}, "shared": {"ff": eff}}
     return {"architecture": "Gemosun", "vocab": sz["vocab"], "width": sz["width"], "norm": {"eps": 1e-5},

@@ -52,8 +52,8 @@ CONFIGS = {
     "odd": config([att(dim=10, heads=3, kv=3, size=1, pool=1, rot=10, yarn=None, scale=0.4, mlp=moe(experts=6, top=3, ff=20, groups=(3, 2), shared=12)),
                    att(dim=10, heads=3, kv=3, size=5, pool=5, rot=4, scale=0.4, mlp=dense(36)),
                    att(dim=6, heads=2, kv=1, size=0, pool=0, rot=0, scale=0.5, mlp=moe(experts=5, top=1, ff=8, groups=(5, 3), shared=8))], vocab=33, width=44, eps=1e-3),
-    "wide": config([att(dim=32, heads=6, kv=1, size=16, pool=16, rot=32, base=5000.0, scale=0.11, mlp=moe(experts=16, top=4, ff=32, groups=(2, 1), shared=32)),
-                    att(dim=32, heads=6, kv=2, size=40, pool=8, rot=12, scale=0.11, mlp=dense(72))], vocab=130, width=96),
+    "wide": config([att(dim=32, heads=6, kv=1, size=16, pool=16, rot=32, base=5000.0, scale=0.11, mlp=moe(experts=12, top=3, ff=32, groups=(3, 1), shared=40)),
+                    att(dim=32, heads=6, kv=2, size=36, pool=8, rot=12, scale=0.11, mlp=dense(72))], vocab=130, width=96),
 }
 
 
@@ -234,7 +234,7 @@ def test_alone_and_in_a_batch_agree(cases):
 @pytest.mark.parametrize("what,delta", [("size", 1), ("size", -1), ("pool", 1)])
 def test_window_and_pool_edges_seen_through_the_whole_model(cases, what, delta):
     """tokens decoded alone where the first key leaves the window and where the first pooled block appears; the same weights with a
-    window (or a block) one position off give logits that differ there by far more than the tolerance, so a mask that is one off
+    window (or a block) one position off give logits that differ there by many times the tolerance, so a mask that is one off
     cannot pass"""
     c = cases("wide")
     t = toks(70, c.cfg["vocab"], 6)
@@ -250,7 +250,7 @@ def test_window_and_pool_edges_seen_through_the_whole_model(cases, what, delta):
     wrong = copy.deepcopy(c.cfg)
     wrong["layers"][0]["mixer"]["mask"][what] += delta
     off = O.forward(wrong, c.P, t[:size + pool + 3])
-    assert err(off[size - 2:], ref[size - 2:size + pool + 3]) > 100 * TOL32
+    assert err(off[size - 2:], ref[size - 2:size + pool + 3]) > 20 * TOL32
 
 
 def test_greedy_generation_through_the_scheduler(cases):

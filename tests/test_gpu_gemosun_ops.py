@@ -234,7 +234,7 @@ def test_pooled_block_far_back_among_hundreds(ops):
 
 
 # ---- mixture of experts ----------------------------------------------------------------------------------------------------------------
-@pytest.mark.parametrize("T,E,top,groups,keep", [(7, 8, 2, 4, 2), (40, 16, 4, 2, 1), (3, 6, 3, 3, 2), (5, 5, 1, 5, 3), (9, 12, 5, 1, 1), (2, 64, 8, 8, 4), (4, 3, 3, 1, 1)])
+@pytest.mark.parametrize("T,E,top,groups,keep", [(7, 8, 2, 4, 2), (40, 16, 5, 2, 1), (3, 6, 3, 3, 2), (5, 5, 1, 5, 3), (9, 12, 5, 1, 1), (2, 64, 8, 8, 4), (4, 3, 3, 1, 1)])
 def test_router_choice_and_weights(ops, T, E, top, groups, keep):
     z = rnd(T, E + 2, seed=80, scale=2.0)
     ids = torch.full((T * top,), -1, dtype=torch.int32, device=DEV)
