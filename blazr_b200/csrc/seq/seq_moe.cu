@@ -30,15 +30,12 @@ __global__ void moe_gather_kernel(const __nv_bfloat16* __restrict__ x, int64_t l
     }
 }
 
-// grid (T), one warp per token
-__global__ void moe_route_kernel(const float* __restrict__ z, int64_t ldz, int E, int groups, int keep, int top, int32_t* __restrict__ ids,
-                                 float* __restrict__ wts, int32_t* __restrict__ counts) {
-    extern __shared__ float sm[];
+// choice of one token by one warp: zr = its E router logits; sm = 2 * E + groups floats of shared memory
+__device__ __forceinline__ void route_token(const float* zr, float* sm, int t, int lane, int E, int groups, int keep, int top, int32_t* __restrict__ ids,
+                                            float* __restrict__ wts, int32_t* __restrict__ counts) {
     float* s = sm;            // [E] scores; a chosen or excluded expert is marked by a negative value in `avail`
     float* avail = sm + E;    // [E]
     float* gsc = avail + E;   // [groups]
-    const int t = blockIdx.x, lane = threadIdx.x;
-    const float* zr = z + (int64_t)t * ldz;
     for (int e = lane; e < E; e += 32) {
         const float v = sigmoidf_acc(zr[e]);
         s[e] = v, avail[e] = v;
@@ -98,6 +95,56 @@ __global__ void moe_route_kernel(const float* __restrict__ z, int64_t ldz, int E
     const float inv = 1.0f / (sum + 1e-20f);
     __syncwarp();
     for (int k = lane; k < top; k += 32) wts[(int64_t)t * top + k] *= inv;
+}
+
+// grid (T), one warp per token
+__global__ void moe_route_kernel(const float* __restrict__ z, int64_t ldz, int E, int groups, int keep, int top, int32_t* __restrict__ ids,
+                                 float* __restrict__ wts, int32_t* __restrict__ counts) {
+    extern __shared__ float sm[];
+    route_token(z + (int64_t)blockIdx.x * ldz, sm, blockIdx.x, threadIdx.x, E, groups, keep, top, ids, wts, counts);
+}
+
+__device__ __forceinline__ void bf16x8_f32(const uint4 v, float* f);
+template <typename XT>
+__device__ __forceinline__ float ldx(const XT* p);
+
+// Router of a step of few tokens in one kernel: grid (T), 8 warps.  The warps share out the NR rows of the router weight (the E experts'
+// rows and any rows stacked behind them), z[t][n] = x[t] . w[n] goes to memory and to shared memory, then warp 0 makes the token's choice.
+template <typename XT, bool VEC>
+__global__ void __launch_bounds__(256) moe_router_rows_kernel(const XT* __restrict__ x, int64_t ldx_, const __nv_bfloat16* __restrict__ w, int NR, int K,
+                                                              float* __restrict__ z, int64_t ldz, int E, int groups, int keep, int top,
+                                                              int32_t* __restrict__ ids, float* __restrict__ wts) {
+    extern __shared__ float sm[];   // NR logits, then the choice's 2 * E + groups floats
+    const int t = blockIdx.x, lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const XT* xr = x + (int64_t)t * ldx_;
+    for (int n = wid; n < NR; n += 8) {
+        const __nv_bfloat16* wr = w + (int64_t)n * K;
+        float acc = 0.f;
+        if (VEC) {
+#pragma unroll 4
+            for (int k = lane * 8; k < K; k += 256) {
+                float wv[8], xv[8];
+                bf16x8_f32(__ldg(reinterpret_cast<const uint4*>(wr + k)), wv);
+                if (sizeof(XT) == 4) {
+                    const float4 q0 = __ldg(reinterpret_cast<const float4*>(xr + k)), q1 = __ldg(reinterpret_cast<const float4*>(xr + k) + 1);
+                    xv[0] = q0.x, xv[1] = q0.y, xv[2] = q0.z, xv[3] = q0.w, xv[4] = q1.x, xv[5] = q1.y, xv[6] = q1.z, xv[7] = q1.w;
+                } else {
+                    bf16x8_f32(__ldg(reinterpret_cast<const uint4*>(xr + k)), xv);
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc = fmaf(wv[i], xv[i], acc);
+            }
+        } else {
+            for (int k = lane; k < K; k += 32) acc = fmaf(__bfloat162float(wr[k]), ldx<XT>(xr + k), acc);
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) {
+            sm[n] = acc;
+            z[(int64_t)t * ldz + n] = acc;
+        }
+    }
+    __syncthreads();
+    if (wid == 0) route_token(sm, sm + NR, t, lane, E, groups, keep, top, ids, wts, nullptr);
 }
 
 // grid (E), 256 threads: block e places the pairs of expert e behind those of the experts before it, in pair order
@@ -318,6 +365,31 @@ int b200seq_moe_route(const float* z, int64_t ldz, int T, int E, int groups, int
     const int g = groups > 1 ? groups : 1;
     moe_route_kernel<<<T, 32, (size_t)(2 * E + g) * sizeof(float), cs>>>(z, ldz, E, g, groups > 1 ? keep : 1, top, ids, wts, counts);
     SEQ_LAUNCH_CHECK("moe_route");
+    return 0;
+}
+
+int b200seq_moe_router(const void* x, int x_dtype, int64_t ldx_, const void* w, int T, int NR, int K, int E, int groups, int keep, int top, float* z, int64_t ldz,
+                       int32_t* ids, float* wts, void* stream) {
+    if (!x || !w || !z || !ids || !wts || T < 0 || T > 8 || E < 1 || E > MOE_MAX_E || NR < E || K < 1 || ldx_ < K || ldz < NR || top < 1 || top > E)
+        return fail(B200SEQ_ERR_INVALID_ARG, "moe_router: bad arguments (at most 8 tokens, experts <= %d)", MOE_MAX_E);
+    if (groups > 1 && (E % groups || keep < 1 || keep > groups || (int64_t)keep * (E / groups) < top))
+        return fail(B200SEQ_ERR_INVALID_ARG, "moe_router: groups must divide the experts and the kept groups must hold `top` experts");
+    if (x_dtype != B200SEQ_F32 && x_dtype != B200SEQ_BF16) return fail(B200SEQ_ERR_INVALID_ARG, "moe_router: activation dtype");
+    if (T == 0) return 0;
+    const int g = groups > 1 ? groups : 1, kp = groups > 1 ? keep : 1;
+    const size_t smem = (size_t)(NR + 2 * E + g) * sizeof(float);
+    const size_t es = x_dtype == B200SEQ_F32 ? 4 : 2;
+    const bool vec = K % 8 == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (ldx_ * es) % 16 == 0;
+    cudaStream_t cs = (cudaStream_t)stream;
+    const __nv_bfloat16* wb = (const __nv_bfloat16*)w;
+    if (x_dtype == B200SEQ_F32) {
+        if (vec) moe_router_rows_kernel<float, true><<<T, 256, smem, cs>>>((const float*)x, ldx_, wb, NR, K, z, ldz, E, g, kp, top, ids, wts);
+        else moe_router_rows_kernel<float, false><<<T, 256, smem, cs>>>((const float*)x, ldx_, wb, NR, K, z, ldz, E, g, kp, top, ids, wts);
+    } else {
+        if (vec) moe_router_rows_kernel<__nv_bfloat16, true><<<T, 256, smem, cs>>>((const __nv_bfloat16*)x, ldx_, wb, NR, K, z, ldz, E, g, kp, top, ids, wts);
+        else moe_router_rows_kernel<__nv_bfloat16, false><<<T, 256, smem, cs>>>((const __nv_bfloat16*)x, ldx_, wb, NR, K, z, ldz, E, g, kp, top, ids, wts);
+    }
+    SEQ_LAUNCH_CHECK("moe_router");
     return 0;
 }
 

@@ -90,6 +90,7 @@ class Engine:
         """entries: [{"id", "tokens", "want"}]; end: requests whose pages and slot are given back after the step.
         Returns the logits of the wanted places as a host array, or None when nothing was wanted."""
         out = None
+        entries = [e for e in entries if len(e.get("tokens", ()))]      # an entry that brings no token has nothing to run
         if entries:
             logits = self._forward([(str(e["id"]), list(e["tokens"]), list(e.get("want", ()))) for e in entries])
             if logits.shape[0]:

@@ -337,7 +337,7 @@ class LayeredModel:
         self._graphs: Dict[int, object] = {}
         self.use_graphs = True
         self.overlap_branches = True     # depth layout: mixer and feed-forward of a layer on two streams
-        self._side = None
+        self._side = self._side2 = None
 
     # ---- cache and state -------------------------------------------------------------------------------------------------------
     def allocate(self, num_blocks: int, block_size: int, max_seqs: int, max_seq_tokens: int) -> None:
@@ -482,19 +482,20 @@ class LayeredModel:
             ops.depth_norm(x0, a1, L0["norm1"], cfg.eps, out2=a2 if L0["spec"].ff is not None else None, w2=L0.get("norm2"))
         x_cur = x0
         # the two branches of a layer read the same input and do not depend on one another: the feed-forward runs on a second stream
-        # beside the mixer (inside a captured decode step they become parallel branches of the graph).  Not while operators are timed alone.
+        # beside the mixer, a shared expert on a third beside the routed ones (inside a captured decode step they become parallel branches
+        # of the graph).  Not while operators are timed alone.
         two_streams = self.overlap_branches and self.dev.type == "cuda" and seqops.timeline is None
         if two_streams and self._side is None:
-            self._side = torch.cuda.Stream(self.dev)
+            self._side, self._side2 = torch.cuda.Stream(self.dev), torch.cuda.Stream(self.dev)
         for i, L in enumerate(self.layers):
             ls: LayerSpec = L["spec"]
             if ls.kind != "attention":
                 raise ValueError("the depth-averaged layout is wired for attention mixers")
             has_ff = ls.ff is not None
 
-            def feed_forward():
+            def feed_forward(shared_done=None):
                 if isinstance(ls.ff, MoeFfSpec):
-                    self._moe_ff(L, ls.ff, ws, T, a2, y2)
+                    self._moe_ff(L, ls.ff, ws, T, a2, y2, shared_done)
                 else:
                     self._dense_ff(L, ls.ff, ws, T, a2, y2, inner=ws.ff_inner, proj=ws.ff_proj)
 
@@ -502,9 +503,16 @@ class LayeredModel:
                 main = torch.cuda.current_stream(self.dev)
                 fork, join = torch.cuda.Event(), torch.cuda.Event()
                 fork.record(main)
+                shared_done = None
+                if isinstance(ls.ff, MoeFfSpec) and ls.ff.shared_ff:      # the shared expert does not wait for the router either: a third stream
+                    shared_done = torch.cuda.Event()
+                    self._side2.wait_event(fork)
+                    with torch.cuda.stream(self._side2):
+                        self._shared_expert(L, ls.ff, ws, T, a2)
+                        shared_done.record(self._side2)
                 self._side.wait_event(fork)
                 with torch.cuda.stream(self._side):
-                    feed_forward()
+                    feed_forward(shared_done)
                     join.record(self._side)
                 self._attention(L, ls.mixer, ws, st, T, a1, y1)
                 main.wait_event(join)
@@ -600,15 +608,19 @@ class LayeredModel:
 
     MOE_ROW_PAIRS = 64      # up to this many (token, choice) pairs the experts' weights are streamed per pair; more: tiles over sorted pairs
 
-    def _moe_ff(self, L, f: "MoeFfSpec", ws: _Workspace, T: int, a: torch.Tensor, y: torch.Tensor) -> None:
+    def _moe_ff(self, L, f: "MoeFfSpec", ws: _Workspace, T: int, a: torch.Tensor, y: torch.Tensor, shared_done=None) -> None:
+        """shared_done: event after which the shared expert's output is in ws.moe_sh (it ran elsewhere); None: it runs here"""
         ops = seqops
         E, top = f.experts, f.top
         gated_shared = bool(f.shared_ff and f.shared_gate)
         z = ws.moe_z[:T, :L["w_router"].shape[0]]
-        ops.linear(a, L["w_router"], z)
         pairs = T * top
         rows_form = pairs <= self.MOE_ROW_PAIRS
-        ops.moe_route(z, E, f.groups, f.keep, top, ws.moe_ids, ws.moe_wts, None if rows_form else ws.moe_cnt)
+        if T <= 8 and rows_form:        # few tokens: projection and choice in one kernel
+            ops.moe_router(a, L["w_router"], E, f.groups, f.keep, top, z, ws.moe_ids, ws.moe_wts)
+        else:
+            ops.linear(a, L["w_router"], z)
+            ops.moe_route(z, E, f.groups, f.keep, top, ws.moe_ids, ws.moe_wts, None if rows_form else ws.moe_cnt)
         kind = ops.ACT_KINDS[f.act]
         mid = ws.moe_act.view(-1)[:pairs * f.ff].view(pairs, f.ff)
         ys = ws.moe_ys[:pairs]
@@ -625,9 +637,16 @@ class LayeredModel:
             ops.moe_linear(a, top, L["w_eup"], ws.moe_ids, order, offs, pairs, kind, mid)
         ops.moe_linear(mid, 0, L["w_edown"], ws.moe_ids, order, offs, pairs, ops.ACT_NONE, ys)
         sh = None
-        if f.shared_ff:
-            smid = ws.ff_inner.view(-1)[:T * f.shared_ff].view(T, f.shared_ff)
-            self._proj_act(ws.ff_proj, T, a, L["w_sup"], kind, smid)
+        if shared_done is not None:
+            torch.cuda.current_stream(self.dev).wait_event(shared_done)
             sh = ws.moe_sh[:T]
-            ops.linear(smid, L["w_sdown"], sh)
+        elif f.shared_ff:
+            sh = self._shared_expert(L, f, ws, T, a)
         ops.moe_combine(ys, ws.moe_wts, slot, T, top, sh, z[:, E] if gated_shared else None, y)
+
+    def _shared_expert(self, L, f: "MoeFfSpec", ws: _Workspace, T: int, a: torch.Tensor) -> torch.Tensor:
+        smid = ws.ff_inner.view(-1)[:T * f.shared_ff].view(T, f.shared_ff)
+        self._proj_act(ws.ff_proj, T, a, L["w_sup"], seqops.ACT_KINDS[f.act], smid)
+        sh = ws.moe_sh[:T]
+        seqops.linear(smid, L["w_sdown"], sh)
+        return sh

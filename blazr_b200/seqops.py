@@ -34,7 +34,7 @@ _DT = {torch.float32: F32, torch.bfloat16: BF16}
 EXPORTS = ["b200seq_last_error", "b200seq_version", "b200seq_launch_count", "b200seq_error_flags", "b200seq_embed_streams", "b200seq_hc_norm", "b200seq_hc_norm_conv",
            "b200seq_causal_conv", "b200seq_group_rmsnorm", "b200seq_gated_act", "b200seq_linear", "b200seq_linear_gated", "b200seq_attn_prep", "b200seq_attn", "b200seq_attn_scratch_floats",
            "b200seq_ssm_scan", "b200seq_ssm_scratch_floats", "b200seq_argmax", "b200seq_linear_act", "b200seq_act", "b200seq_depth_norm", "b200seq_attn_prep_ex",
-           "b200seq_attn_ex", "b200seq_moe_route", "b200seq_moe_sort", "b200seq_moe_linear", "b200seq_moe_gather", "b200seq_moe_combine"]
+           "b200seq_attn_ex", "b200seq_moe_route", "b200seq_moe_sort", "b200seq_moe_linear", "b200seq_moe_gather", "b200seq_moe_combine", "b200seq_moe_router"]
 
 
 class SeqError(RuntimeError):
@@ -288,6 +288,15 @@ def moe_route(z: torch.Tensor, E: int, groups: int, keep: int, top: int, ids: to
     T, _, ldz = _rows2d(z)
     assert ids.dtype == torch.int32 and wts.dtype == torch.float32 and ids.is_contiguous() and wts.is_contiguous() and ids.numel() >= T * top
     _check(lib().b200seq_moe_route(_p(z), C.c_int64(ldz), T, E, groups, keep, top, _p(ids), _p(wts), _p(counts), _st(z)))
+
+
+@_timed
+def moe_router(x: torch.Tensor, w: torch.Tensor, E: int, groups: int, keep: int, top: int, z: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor):
+    """router projection (all rows of the stacked weight, into z) and the choice among the first E, for at most 8 tokens, in one kernel"""
+    T, K, ldx = _rows2d(x)
+    _, NR, ldz = _rows2d(z)
+    assert w.dtype == torch.bfloat16 and w.is_contiguous() and tuple(w.shape) == (NR, K) and z.dtype == torch.float32 and z.shape[0] == T
+    _check(lib().b200seq_moe_router(_p(x), _DT[x.dtype], C.c_int64(ldx), _p(w), T, NR, K, E, groups, keep, top, _p(z), C.c_int64(ldz), _p(ids), _p(wts), _st(x)))
 
 
 @_timed

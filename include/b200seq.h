@@ -193,6 +193,10 @@ int b200seq_attn_ex(const float* proj, int64_t ld, const b200seq_step* st, const
  * + 1e-20).  counts[E] receives how many (token, choice) pairs every expert got.
  * sort: the pairs p = t * top + j ordered by expert (stable): offs[E + 1] prefix sums, sorted[slot] = p, slot_of[p] = slot. */
 int b200seq_moe_route(const float* z, int64_t ldz, int T, int E, int groups, int keep, int top, int32_t* ids, float* wts, int32_t* counts, void* stream);
+/* Router projection and choice of a step of at most 8 tokens in one kernel: z[t][n] = x[t] . w[n] for the NR >= E rows of the stacked router
+ * weight (bf16 [NR, K]; rows behind the E experts' are projected and left in z for the caller), then the choice of b200seq_moe_route on z[t][0..E). */
+int b200seq_moe_router(const void* x, int x_dtype, int64_t ldx, const void* w_bf16, int T, int NR, int K, int E, int groups, int keep, int top, float* z, int64_t ldz,
+                       int32_t* ids, float* wts, void* stream);
 int b200seq_moe_sort(const int32_t* ids, int pairs, int E, const int32_t* counts, int32_t* offs, int32_t* sorted, int32_t* slot_of, void* stream);
 /* One projection of every pair through its expert's weight: w bf16 [E][N][K].  Row r of the result belongs to pair p = sorted ? sorted[r] : r
  * (sorted + offs from b200seq_moe_sort: tiles of one expert's rows; null: one launch row per pair, weights streamed, for few pairs).

@@ -249,6 +249,25 @@ def test_router_choice_and_weights(ops, T, E, top, groups, keep):
     assert cnt.cpu().tolist() == [int((ids == e).sum()) for e in range(E)]
 
 
+@pytest.mark.parametrize("T,E,extra,top,groups,keep,K,xdt", [(1, 8, 1, 2, 4, 2, 40, torch.float32), (8, 16, 0, 5, 2, 1, 96, torch.bfloat16), (3, 6, 2, 3, 3, 2, 33, torch.float32),
+                                                             (4, 12, 1, 4, 1, 1, 200, torch.bfloat16)])
+def test_router_projection_and_choice_in_one_kernel(ops, T, E, extra, top, groups, keep, K, xdt):
+    """single-token steps: the stacked router weight (experts' rows + rows riding behind them) projected and the choice made at once"""
+    x = rnd(T, K, seed=90).to(xdt)
+    w = rnd(E + extra, K, seed=91, scale=3.0 * K ** -0.5).bfloat16()
+    z = torch.full((T, E + extra + 1), 7.0, device=DEV)
+    ids = torch.full((T * top,), -1, dtype=torch.int32, device=DEV)
+    wts = torch.zeros(T * top, device=DEV)
+    ops.moe_router(x.to(DEV), w.to(DEV), E, groups, keep, top, z[:, :E + extra], ids, wts)
+    zr = x.double() @ w.double().T
+    close(z[:, :E + extra], zr, 5e-6)
+    assert bool((z[:, E + extra:] == 7.0).all())
+    for t in range(T):
+        chosen, wt = O.route(torch.sigmoid(zr[t, :E]), top, groups, keep)
+        assert ids.cpu().view(T, top)[t].tolist() == chosen
+        close(wts.cpu().view(T, top)[t], wt, 2e-6)
+
+
 @pytest.mark.parametrize("T,E,top,N,K,xdt", [(3, 4, 2, 24, 40, torch.float32), (70, 8, 3, 50, 36, torch.float32), (5, 6, 1, 33, 64, torch.bfloat16),
                                              (130, 5, 2, 72, 96, torch.bfloat16), (600, 9, 3, 200, 136, torch.bfloat16)])
 def test_expert_projections_per_pair_and_over_sorted_tiles(ops, T, E, top, N, K, xdt):
