@@ -1,4 +1,4 @@
-"""Host-side builders of the batched-decode inputs (pure Python, no GPU).
+"""Host-side builders of the batched-decode inputs and of flat mixed steps (pure Python, no GPU).
 
 Mirror of reference src/engine/batch_decode.rs:59-131 (`process_decode_batch`): for every decoding sequence the
 last token, the KV slot of the new token (`block * block_size + offset`, -1 when the block table is too short) and its
