@@ -295,6 +295,35 @@ def test_trace_replay_command(cases, tmp_path):
     assert err(g[0], ref[19:20]) < TOL32 and err(g[1], ref[2:3]) < TOL32 and err(g[2], ref[29:30]) < TOL32
 
 
+def test_generate_command(cases, tmp_path):
+    """python -m blazr_b200 generate: the checkpoint's config.json picks the design; greedy tokens follow the restatement"""
+    import json
+    import os
+    import subprocess
+    import sys
+    c = cases("odd")
+    folder = str(tmp_path / "m")
+    O.write_checkpoint(folder, c.cfg, c.P)
+    prompts = [toks(9, c.cfg["vocab"], 60), toks(2, c.cfg["vocab"], 61)]
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, "-m", "blazr_b200", "generate", "--model", folder, "--dtype", "float32", "--max-new", "4"]
+    for p in prompts:
+        cmd += ["--prompt", ",".join(str(t) for t in p)]
+    r = subprocess.run(cmd, cwd=root, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = [json.loads(l) for l in r.stdout.splitlines() if l.startswith("{")]
+    assert [l["prompt"] for l in lines] == prompts
+    for l in lines:
+        seq = list(l["prompt"])
+        assert len(l["tokens"]) == 4
+        for tok in l["tokens"]:
+            lg = O.forward(c.cfg, c.P, seq)[-1]
+            top = torch.topk(lg, 2).values
+            if (top[0] - top[1]).item() >= 1e-3 * lg.std().item():
+                assert int(lg.argmax()) == tok
+            seq.append(tok)
+
+
 CONFIGS["long"] = config([att(dim=24, heads=6, kv=2, size=50, pool=8, rot=24, base=3000.0, scale=0.2, mlp=moe(experts=12, top=3, ff=40, groups=(3, 2), shared=24)),
                           att(dim=16, heads=4, kv=4, size=130, pool=16, rot=8, scale=0.25, mlp=dense(56))], vocab=77, width=64)
 
